@@ -18,8 +18,8 @@
 #define LLMSS_API extern "C" __attribute__((visibility("default")))
 
 enum { LLMSS_F16 = 0, LLMSS_BF16 = 1, LLMSS_F32 = 2 };
-enum { LLMSS_ACT_NONE = 0, LLMSS_ACT_GELU_TANH = 1, LLMSS_ACT_GELU_ERF = 2, LLMSS_ACT_RELU = 3, LLMSS_ACT_SILU = 4 };
-enum { LLMSS_NORM_LAYER = 0, LLMSS_NORM_RMS = 1 };
+enum { LLMSS_ACT_NONE = 0, LLMSS_ACT_GELU_TANH = 1, LLMSS_ACT_GELU_ERF = 2, LLMSS_ACT_RELU = 3, LLMSS_ACT_SILU = 4, LLMSS_ACT_RELU2 = 5 };
+enum { LLMSS_NORM_LAYER = 0, LLMSS_NORM_RMS = 1, LLMSS_NORM_DYT = 2 };
 enum { LLMSS_ROPE_NONE = 0, LLMSS_ROPE_GPTJ = 1, LLMSS_ROPE_NEOX = 2 };
 
 // ---------------------------------------------------------------- host error plumbing
@@ -39,6 +39,15 @@ void llmss_set_error(const char* fmt, ...);
       llmss_set_error(__VA_ARGS__);                                                    \
       return -1;                                                                       \
     }                                                                                  \
+  } while (0)
+
+// run CALL with `T` bound to the element type named by a runtime dtype id (half, bf16 or float)
+#define LLMSS_BY_DTYPE(dtype, CALL)                                                  \
+  do {                                                                               \
+    if ((dtype) == LLMSS_F16) { using T = __half; CALL; }                            \
+    else if ((dtype) == LLMSS_BF16) { using T = __nv_bfloat16; CALL; }               \
+    else if ((dtype) == LLMSS_F32) { using T = float; CALL; }                        \
+    else LLMSS_REQUIRE(false, "bad dtype %d", (int)(dtype));                         \
   } while (0)
 
 // cudaFuncSetAttribute applies to the CURRENT device only: a process that drives several GPUs has to repeat it on
@@ -109,6 +118,7 @@ __device__ __forceinline__ float act_apply(float x, int act) {
     case LLMSS_ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
     case LLMSS_ACT_RELU: return fmaxf(x, 0.0f);
     case LLMSS_ACT_SILU: return x / (1.0f + __expf(-x));
+    case LLMSS_ACT_RELU2: { const float r = fmaxf(x, 0.0f); return r * r; }
     default: return x;
   }
 }

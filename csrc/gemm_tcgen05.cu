@@ -170,6 +170,7 @@ __device__ __forceinline__ float act_fast(float x, int act) {
   if (act == LLMSS_ACT_RELU) return fmaxf(x, 0.0f);
   if (act == LLMSS_ACT_SILU) return __fdividef(x, 1.0f + __expf(-x));
   if (act == LLMSS_ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
+  if (act == LLMSS_ACT_RELU2) { const float r = fmaxf(x, 0.0f); return r * r; }
   return x;
 }
 

@@ -175,6 +175,49 @@ int llmss_attn_decode_static(const void* q, int64_t ldq, const void* k_cache, co
                              int B, int hq, int hkv, int d, int block_size, float scale, int num_splits, int dtype,
                              llmss_stream_t stream);
 
+/* ---- 32-bit residual stream + Dynamic Tanh (y = tanh(alpha x) w + b; no statistics) ----
+ * res_out = res_in + s1 * a + s2 * b (a, b: 32-bit branch outputs, s1 / s2: per-feature layer scales or null);
+ * out = DyT(res_out) in `dtype` (0 half, 1 bf16, 2 float); res_out may alias res_in; out / res_out may be null. */
+int llmss_dyt_residual(const float* res_in, float* res_out, const float* a, const void* s1, const float* b, const void* s2,
+                       const void* w, const void* bias, void* out, float alpha, int M, int H, int64_t ldr, int64_t lda,
+                       int64_t ldb, int64_t ldo, int dtype, llmss_stream_t stream);
+/* token (+ learned position) embedding summed and stored in 32-bit */
+int llmss_embed_f32(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int T, int H,
+                    int vocab, int max_pos, int pos_offset, int64_t ldo, int dtype, llmss_stream_t stream);
+/* out[:, :Ha] = cast(a), out[:, Ha:] = cast(b): 32-bit streams -> one GEMM operand */
+int llmss_cast_concat(const float* a, const float* b, void* out, int M, int Ha, int Hb, int64_t lda, int64_t ldb, int64_t ldo,
+                      int dtype, llmss_stream_t stream);
+
+/* ---- strided batched GEMM on the CUDA cores (true 32-bit layers, unaligned 16-bit layers, per-head products) ----
+ * out(t,h,n) = act(sum_k x[t*ldx + h*sxh + k] * w[h*swh + k*swk + n*swn] + bias[n]) * row_scale[t*lds + h] */
+int llmss_bgemm_simt(const void* x, int64_t ldx, int64_t sxh, const void* w, int64_t swh, int64_t swk, int64_t swn,
+                     const void* bias, const float* row_scale, int64_t lds, void* out, int64_t ldo, int64_t soh, int M, int N,
+                     int K, int H, int act, int act_start, int dtype, int out_f32, llmss_stream_t stream);
+
+/* ---- latent (low-rank KV) attention, absorbed form, paged cache [num_blocks, block_size, R] ----
+ * prep: y is the 32-bit output of the fused input projection; columns [c_off, c_off + R) are RMS-normed with norm_w and
+ * written to the cache slot of each token (slot < 0: not written), columns [q_off, q_off + n_q) are cast to q_out, columns
+ * [g_off, g_off + H) go through a sigmoid into gate [T, H] (gate may be null). */
+int llmss_latent_prep(const float* y, int64_t ldy, int q_off, int c_off, int g_off, int n_q, int R, int H, const void* norm_w,
+                      float eps, const int* slots, void* cache, void* q_out, int64_t ldq, float* gate, int T, int dtype,
+                      llmss_stream_t stream);
+int64_t llmss_latent_attn_scratch_floats(int T, int H, int R, int splits);
+/* q: absorbed queries [T, H * R] (32-bit); token i of sequence b sees cache positions 0 .. seq_lens[b] - q_len_b + i */
+int llmss_latent_attn(const float* q, int64_t ldq, const void* cache, const int* block_tables, int max_blocks, int block_size,
+                      const int* seq_lens, const int* cu_q, void* out, int64_t ldo, float* scratch, int T, int num_seqs,
+                      int max_q, int H, int R, float scale, int splits, int dtype, llmss_stream_t stream);
+
+/* ---- routed mixture of experts ----
+ * route: softmax over E logits, group-limited top-k (ids / wts: [T, top]; dense: optional [T, E], 0 = not chosen) */
+int llmss_moe_route(const float* z, int64_t ldz, int T, int E, int top, int groups, int keep, float route_scale, int* ids,
+                    float* wts, float* dense, llmss_stream_t stream);
+/* out[t] = sum_k wts[t,k] * W_down[ids[t,k]] act(W_up[ids[t,k]] h[t]); w_up [E, F, W]; w_down [W, E * F] (the experts' down matrices side by side,
+ * row stride ldd); act_scratch [T, top, F] */
+int llmss_moe_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up, const void* w_down,
+                      int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T, int W, int F, int top, int act, int dtype,
+                      llmss_stream_t stream);
+int llmss_moe_scale(void* a, int64_t lda, const float* dense, int T, int E, int F, int dtype, llmss_stream_t stream);
+
 /* ---- K10 embedding gather (G1; layers.py:182-214) ---- */
 int llmss_embed(const int* tokens, const int* positions, const void* wte, const void* wpe, void* out, int T, int H,
                 int vocab, int max_pos, int pos_offset, int64_t ldo, int dtype, llmss_stream_t stream);

@@ -56,13 +56,14 @@ class Engine:
                  block_size: Optional[int] = None,
                  num_blocks: Optional[int] = None, use_cuda_graph: Optional[bool] = None,
                  max_prefill_tokens: int = 16384, eos_token_id: Optional[int] = None,
-                 prefill_chunk: Optional[int] = None, sliding_window: bool = False, prefix_cache: bool = False):
+                 prefill_chunk: Optional[int] = None, sliding_window: bool = False, prefix_cache: bool = False,
+                 pool_tokens: Optional[int] = None):
         self.model = model
         self.core = model.core if hasattr(model, "core") else model
         self.comm = self.core.comm
         self.runner = ModelRunner(self.core, max_batch=max_batch, max_seq_len=max_seq_len, block_size=block_size,
                                   num_blocks=num_blocks, use_cuda_graph=use_cuda_graph, prefill_chunk=prefill_chunk,
-                                  sliding_window=sliding_window, prefix_cache=prefix_cache)
+                                  sliding_window=sliding_window, prefix_cache=prefix_cache, pool_tokens=pool_tokens)
         self.max_batch = max_batch
         self.max_prefill_tokens = max_prefill_tokens
         self.eos_token_id = eos_token_id
@@ -78,7 +79,7 @@ class Engine:
     def from_pretrained(cls, path: str, dtype=torch.bfloat16, device=None, process_group=None,
                         symmetric_bytes: int = 128 << 20, lamport_bytes: int = 64 << 20, fuse_parallel: bool = True,
                         **kw) -> "Engine":
-        from transformers import AutoConfig
+        from ..utils.config import load_config
 
         if process_group is None:
             process_group = FakeGroup(0, 1)
@@ -87,7 +88,7 @@ class Engine:
         device = torch.device(device)
         if device.type == "cpu" and dtype in (torch.float16, torch.bfloat16):
             dtype = torch.float32  # CPU oracle path runs in fp32
-        config = AutoConfig.from_pretrained(path)
+        config = load_config(path)
         comm = comm_for(process_group, device)
         if device.type == "cuda" and comm.size > 1 and comm.symm is None:
             comm.attach_symmetric(symmetric_bytes, lamport_bytes)
@@ -129,6 +130,36 @@ class Engine:
         for rid in dropped:
             self.stats.pop(rid, None)
         return dropped
+
+    # ------------------------------------------------------------------ teacher-forced streams
+    def feed(self, entries, end=()) -> torch.Tensor:
+        """One step of given tokens, nothing sampled.  ``entries``: [(key, tokens, want)] -- request ``key`` (admitted at
+        its first entry, one of at most ``max_batch`` live ones) continues with ``tokens``; ``want`` lists the places
+        among them whose logits are returned ([n_wanted, vocab] fp32, in entry order).  All entries run as ONE batch
+        through the runner's packed step.  ``end``: keys whose cache pages go back to the pool after the step."""
+        if not hasattr(self, "streams"):
+            self.streams: Dict[object, SeqState] = {}
+        seqs, toks, want = [], [], []
+        for key, tokens, w in entries:
+            s = self.streams.get(key)
+            if s is None:
+                if len(self.streams) + len(self.running) >= self.max_batch:
+                    raise RuntimeError(f"no free slot for request {key!r}: {self.max_batch} are live")
+                s = self.streams[key] = SeqState(self._next_id, [], SamplingParams(), eos=None)
+                self._next_id += 1
+                METRICS.inc("requests_total")
+            if len(tokens) == 0:
+                continue
+            seqs.append(s)
+            toks.append([int(t) for t in tokens])
+            want.append([int(j) for j in w])
+        out = self.runner.forward_tokens(seqs, toks, want) if seqs else None
+        for key in end:
+            s = self.streams.pop(key, None)
+            if s is not None:
+                self.runner.release(s)
+                METRICS.inc("requests_finished")
+        return out
 
     # ------------------------------------------------------------------ scheduling
     def _admit(self) -> List[SeqState]:

@@ -29,6 +29,35 @@ class KVCache:
     def bytes_per_block(num_layers, block_size, kv_heads, head_dim, dtype) -> int:
         return num_layers * 2 * block_size * kv_heads * head_dim * torch.empty((), dtype=dtype).element_size()
 
+    def copy_blocks_from(self, old: "KVCache", src: int, dst: int, n: int):
+        self.data[:, :, dst:dst + n] = old.data[:, :, src:src + n]
+
+
+class LatentCache:
+    """Paged cache of latent-attention layers: ONE vector per token and layer run (the RMS-normed down-projection
+    from which keys and values of every head are re-derived), instead of a key and a value per head.
+
+    ``ranks[i]`` is the latent width of layer run i -- a layer that is run several times (weight-shared loop) owns
+    one plane per pass, since each pass sees different activations.  Plane layout ``[num_blocks, block_size, rank]``
+    equals the multi-head layout ``[num_blocks, kv_heads = 1, block_size, head_dim = rank]``, so the same block
+    tables, slot mapping and allocator serve it, and the multi-query tcgen05 kernels can read it."""
+
+    def __init__(self, ranks, num_blocks: int, block_size: int, dtype, device):
+        self.ranks, self.num_blocks, self.block_size = list(ranks), num_blocks, block_size
+        self.num_layers = len(self.ranks)
+        self.planes = [torch.zeros(num_blocks, block_size, r, dtype=dtype, device=device) for r in self.ranks]
+
+    def latent(self, run: int) -> torch.Tensor:
+        return self.planes[run]
+
+    @staticmethod
+    def bytes_per_block(ranks, block_size, dtype) -> int:
+        return sum(ranks) * block_size * torch.empty((), dtype=dtype).element_size()
+
+    def copy_blocks_from(self, old: "LatentCache", src: int, dst: int, n: int):
+        for mine, theirs in zip(self.planes, old.planes):
+            mine[dst:dst + n] = theirs[src:src + n]
+
 
 class BlockAllocator:
     """Reference-counted free-list allocator over cache blocks (block 0 is reserved as the padding target).

@@ -23,7 +23,7 @@ from .. import ops
 from ..models.decoder import DecoderLM
 from ..utils.metrics import METRICS
 from .batch import BatchInput
-from .kv_cache import BlockAllocator, KVCache
+from .kv_cache import BlockAllocator
 
 _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -80,7 +80,7 @@ class ModelRunner:
     def __init__(self, core: DecoderLM, max_batch: int = 64, max_seq_len: Optional[int] = None,
                  block_size: Optional[int] = None, num_blocks: Optional[int] = None,
                  use_cuda_graph: Optional[bool] = None, prefill_chunk: Optional[int] = None,
-                 sliding_window: bool = False, prefix_cache: bool = False):
+                 sliding_window: bool = False, prefix_cache: bool = False, pool_tokens: Optional[int] = None):
         self.core, self.spec = core, core.spec
         self.device, self.dtype = core.device, core.dtype
         self.max_batch = max_batch
@@ -93,14 +93,14 @@ class ModelRunner:
         # position table cannot index past it, so they keep stopping at max_seq_len.
         self.sliding = bool(sliding_window) and not self.spec.learned_pos
         if block_size is None:
-            # 64-token pages = one key tile of the tcgen05 decode-attention kernel (one TMA op per K / V
-            # tile); the CPU oracle path and head sizes the kernel does not cover keep 16.
-            block_size = 64 if (self.device.type == "cuda" and core.d in (64, 128, 256)) else 16
+            block_size = core.default_block_size()   # the page size the model's attention kernels like best
         self.block_size = block_size
         self.max_blocks_per_seq = -(-self.max_seq_len // block_size)
+        if num_blocks is None and pool_tokens:
+            num_blocks = 1 + -(-pool_tokens // block_size)    # a pool for this many live tokens, in whole pages
         if num_blocks is None:
             num_blocks = 1 + max_batch * self.max_blocks_per_seq
-        self.kv = KVCache(self.spec.n_layers, num_blocks, block_size, core.hkv, core.d, self.dtype, self.device)
+        self.kv = core.make_cache(num_blocks, block_size)   # multi-head K / V pages, or latent planes: the model knows
         self.alloc = BlockAllocator(num_blocks)
         self._outstanding = 0   # blocks reserved at admission and not yet allocated
         # Prefix cache: full prompt blocks stay registered after their sequence has gone; a later prompt that starts with
@@ -250,6 +250,41 @@ class ModelRunner:
         self._outstanding -= seq.reserved
         seq.reserved = 0
 
+    # ------------------------------------------------------------------ packed steps
+    def _run_packed(self, token_lists, context_lens, block_tables, rows=None) -> torch.Tensor:
+        """THE step function for anything that is not a graph-replayed decode step: sequence i is fed
+        ``token_lists[i]`` on top of ``context_lens[i]`` cached tokens (any mix of whole prompts, portions of prompts
+        and single tokens; the attention op picks its kernel from the batch shape).  Returns fp32 logits, one row
+        per sequence (its last token), or for the packed row indices ``rows``."""
+        batch = BatchInput.build(token_lists, context_lens, block_tables, self.block_size, self.device,
+                                 max_blocks=self.max_blocks_per_seq, pad_to=self.core.tp * 16 if self.core.tp > 1 else 1)
+        self.stats["prefill_tokens"] += int(batch.tokens.numel())
+        if rows is None:
+            return self.core.forward(batch, self.kv, last_only=True)
+        hidden = self.core.forward_hidden(batch, self.kv)
+        idx = torch.tensor(rows, dtype=torch.int64).to(self.device)
+        return self.core.logits(hidden.index_select(0, idx))
+
+    @torch.no_grad()
+    def forward_tokens(self, seqs: Sequence[SeqState], token_lists: Sequence[Sequence[int]],
+                       want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Teacher-forced mixed step: feed ``token_lists[i]`` to ``seqs[i]`` (which continues from the ``length`` tokens
+        it has in the cache; cache pages are taken from the pool as it grows) and return the fp32 logits
+        [sum(len(want[i])), vocab] at the places ``want[i]`` (indices into ``token_lists[i]``; default: each last token).
+        Nothing is sampled and ``output`` is not touched: scoring, replaying recorded schedules, speculative checks."""
+        for s, toks in zip(seqs, token_lists):
+            if s.length + len(toks) > self.max_seq_len:
+                raise ValueError(f"sequence {s.seq_id}: {s.length} + {len(toks)} tokens exceed max_seq_len {self.max_seq_len}")
+            self._grow(s, s.length + len(toks))
+        rows, base = [], 0
+        for i, toks in enumerate(token_lists):
+            rows += [base + j for j in (want[i] if want is not None else [len(toks) - 1])]
+            base += len(toks)
+        logits = self._run_packed(token_lists, [s.length for s in seqs], [s.blocks for s in seqs], rows)
+        for s, toks in zip(seqs, token_lists):
+            s.length += len(toks)
+        return logits[:, :self.spec.vocab]
+
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
     def prefill(self, seqs: Sequence[SeqState], rng_steps: Optional[Sequence[int]] = None) -> List[int]:
@@ -269,16 +304,11 @@ class ModelRunner:
         final_logits = [None] * len(seqs)
         for r in range(rounds):
             live = [(i, s) for i, s in enumerate(seqs) if todo[i] > r * chunk]
-            batch = BatchInput.build([s.prompt[have[i] + r * chunk:have[i] + (r + 1) * chunk] for i, s in live],
-                                     [have[i] + r * chunk for i, _ in live],
-                                     [s.blocks for _, s in live], self.block_size, self.device,
-                                     max_blocks=self.max_blocks_per_seq,
-                                     pad_to=self.core.tp * 16 if self.core.tp > 1 else 1)
-            logits = self.core.forward(batch, self.kv, last_only=True)
+            logits = self._run_packed([s.prompt[have[i] + r * chunk:have[i] + (r + 1) * chunk] for i, s in live],
+                                      [have[i] + r * chunk for i, _ in live], [s.blocks for _, s in live])
             for row, (i, s) in enumerate(live):
                 if todo[i] <= (r + 1) * chunk:
                     final_logits[i] = logits[row]
-            self.stats["prefill_tokens"] += int(batch.tokens.numel())
         if self.prefix_enabled:
             for s in seqs:
                 self._register_blocks(s, s.prompt)
@@ -421,6 +451,8 @@ class ModelRunner:
             return 1
         if Bp in self._tuned_splits:
             return self._tuned_splits[Bp]
+        if not hasattr(self.core, "hkv"):
+            return 0    # models without multi-head K / V pages pick their own split per call
         from ..ops import cuda_impl as cu
 
         return cu.decode_splits(Bp, self.core.hq, self.core.hkv, self.core.d, self.max_seq_len, self.dtype,
@@ -431,6 +463,8 @@ class ModelRunner:
         (batch bucket, heads per rank, current context length) and keep the fastest.  Read-only on the
         KV cache; ~1 ms once per captured graph."""
         c = self.core
+        if not hasattr(c, "hkv"):
+            return 0
         if not self.cuda or c.d not in (64, 128, 256):
             return 1
         from ..ops import cuda_impl as cu

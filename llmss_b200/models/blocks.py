@@ -1,0 +1,94 @@
+"""Sub-layer blocks that are not tied to one model family: latent attention and routed experts.
+
+Each block owns its weights in the layout its kernels want and exposes ``in_rows()`` -- the projection rows
+that read the block's input -- so that a layer can stack the rows of all its blocks into ONE input GEMM
+(the same fusion the multi-head families use for [q | k | v | up]).  All sizes and constants are constructor
+arguments.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..ops import ACT_RELU2
+
+
+class LatentAttention:
+    """Multi-head attention over a low-rank latent, no positional rotation.
+
+        q = W_q h                  [heads * dim]
+        c = rmsnorm(W_dkv h) * g   [rank]           <- the only thing cached
+        k_h = W_uk,h c , v_h = W_uv,h c ;  o_h = softmax(scale * q_h . k_h) v_h   (causal)
+        out = W_o concat_h(gate_h * o_h)            gate = sigmoid(W_g h) per head, if ``gated``
+
+    Executed in the absorbed form (csrc/latent_attn.cu): q~_h = W_uk,h^T q_h, attention with key = value = c,
+    o_h = W_uv,h o~_h.  The output gate rides on the epilogue of the last per-head product."""
+
+    def __init__(self, heads: int, dim: int, vdim: int, rank: int, scale: float, gated: bool, eps: float):
+        self.heads, self.dim, self.vdim, self.rank, self.scale, self.gated, self.eps = heads, dim, vdim, rank, scale, gated, eps
+        self.w_q = self.w_dkv = self.w_g = self.norm_w = self.w_uk = self.w_uv = self.w_o = None
+
+    def in_rows(self):
+        rows = [self.w_q, self.w_dkv] + ([self.w_g] if self.gated else [])
+        return torch.cat(rows, dim=0)
+
+    def bind(self, base: int):
+        """Column offsets of this block's outputs inside the layer's fused projection; returns the next free column."""
+        self.q_off = base
+        self.c_off = base + self.heads * self.dim
+        self.g_off = self.c_off + self.rank if self.gated else -1
+        self.w_q = self.w_dkv = self.w_g = None      # live on inside the layer's fused operand
+        return self.c_off + self.rank + (self.heads if self.gated else 0)
+
+    def forward(self, y, batch, cache, dtype):
+        """y: the layer's fused 32-bit projection [T, *]; returns the block's 32-bit output [T, width]."""
+        H, R = self.heads, self.rank
+        q, gate = ops.latent_prep(y, self.q_off, self.c_off, self.g_off, H * self.dim, R, H, self.norm_w, self.eps,
+                                  batch.slot_mapping, cache, dtype)
+        q_abs = ops.heads_matmul(q, self.w_uk, H, self.dim, R, True, out_dtype=ops.latent_query_dtype(cache, H, R))
+        o_lat = ops.latent_attention(q_abs, cache, batch, H, R, self.scale, dtype)
+        ctx = ops.heads_matmul(o_lat, self.w_uv, H, R, self.vdim, False, row_scale=gate, out_dtype=dtype)
+        return ops.linear(ctx, self.w_o, out_dtype=torch.float32)
+
+
+_DENSE_MIN = int(os.environ.get("LLMSS_MOE_DENSE_MIN_TOKENS", "256"))
+
+
+class RoutedExperts:
+    """Mixture of small feed-forward experts with group-limited top-k routing (csrc/moe.cu).
+
+    Router logits come from the layer's fused input projection (32-bit accumulation).  Short batches gather the
+    chosen experts' weight rows per token; from ``LLMSS_MOE_DENSE_MIN_TOKENS`` tokens on, 16-bit CUDA batches run the
+    dense form: every expert's up-projection in one tensor-core GEMM (activation fused), each expert's block scaled
+    by its routing weight (0 if not chosen), one GEMM over the side-by-side down matrices."""
+
+    def __init__(self, experts: int, top: int, groups: int, keep: int, route_scale: float, ff: int, act: int = ACT_RELU2):
+        if experts % groups or not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
+            raise ValueError(f"routed experts: bad routing sizes experts={experts} groups={groups} keep={keep} top={top}")
+        self.experts, self.top, self.groups, self.keep, self.route_scale, self.ff, self.act = experts, top, groups, keep, route_scale, ff, act
+        self.w_router = self.w_up = self.w_down = None     # [E, W] | [E, F, W] | [W, E * F]
+
+    def in_rows(self):
+        return self.w_router
+
+    def bind(self, base: int):
+        self.z_off = base
+        self.w_router = None
+        return base + self.experts
+
+    def forward(self, h, y):
+        E, F = self.experts, self.ff
+        z = y[:, self.z_off:self.z_off + E]
+        T = h.shape[0]
+        if h.is_cuda and h.dtype != torch.float32 and T >= _DENSE_MIN:
+            from ..ops import cuda_impl as cu
+
+            _, _, dense = cu.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale, dense=True)
+            a = ops.linear(h, self.w_up.view(E * F, -1), act=self.act)
+            cu.moe_scale(a, dense, E, F)
+            return ops.linear(a, self.w_down, out_dtype=torch.float32)
+        ids, wts = ops.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale)
+        return ops.moe_experts(h, ids, wts, self.w_up, self.w_down, self.act)

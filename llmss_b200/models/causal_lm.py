@@ -16,7 +16,7 @@ import torch
 from torch import nn
 
 from ..engine.batch import BatchInput
-from ..engine.kv_cache import KVCache
+from .bedovik import BedovikLM, bedovik_spec, load_bedovik
 from .decoder import DecoderLM
 from .families import FAMILIES
 
@@ -33,8 +33,7 @@ class PagedState:
         bs = self.block_size
         self.blocks_per_seq = max(1, -(-capacity // bs))
         self.capacity = self.blocks_per_seq * bs
-        c, s = self.core, self.core.spec
-        self.kv = KVCache(s.n_layers, 1 + self.B * self.blocks_per_seq, bs, c.hkv, c.d, c.dtype, c.device)
+        self.kv = self.core.make_cache(1 + self.B * self.blocks_per_seq, bs)
         self.tables = [[1 + i * self.blocks_per_seq + j for j in range(self.blocks_per_seq)] for i in range(self.B)]
 
     def ensure(self, total_len: int):
@@ -46,7 +45,7 @@ class PagedState:
         for i in range(self.B):
             src = 1 + i * old_bps
             dst = 1 + i * self.blocks_per_seq
-            self.kv.data[:, :, dst:dst + old_bps] = old_kv.data[:, :, src:src + old_bps]
+            self.kv.copy_blocks_from(old_kv, src, dst, old_bps)
 
     def get_seq_length(self) -> int:
         return self.length
@@ -120,10 +119,24 @@ class LlamaForCausalLM(CausalLM):
     family = "llama"
 
 
+class BedovikForCausalLM(CausalLM):
+    """Native architecture (config.json with an ``architecture`` key, see models/bedovik.py): latent attention, routed
+    experts, Dynamic Tanh, weight-shared loop.  Same constructor / forward contract as the HF-shaped classes."""
+    family = "bedovik"
+
+    def __init__(self, config, weights, fuse_parallel: bool = True):
+        nn.Module.__init__(self)
+        self.config = config
+        self.core = BedovikLM(bedovik_spec(config), weights.process_group, weights.device, weights.dtype)
+        load_bedovik(self.core, weights)
+        self.core.finalize()
+
+
 MODEL_REGISTRY = {
     "gptj": GPTJForCausalLM,
     "gpt_bigcode": GPTBigCodeForCausalLM,
     "gpt2": GPT2LMHeadModel,
     "opt": OPTForCausalLM,
     "llama": LlamaForCausalLM,
+    "bedovik": BedovikForCausalLM,
 }

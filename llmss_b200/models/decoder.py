@@ -129,6 +129,17 @@ class DecoderLM(nn.Module):
         self.layers: List[LayerWeights] = []
         self.wte = self.wpe = self.lnf_w = self.lnf_b = self.w_head = self.b_head = None
 
+    # ------------------------------------------------------------------ cache
+    def default_block_size(self) -> int:
+        """64-token pages = one key tile of the tcgen05 decode-attention kernel (one TMA op per K / V tile); the CPU
+        oracle path and head sizes the kernel does not cover keep 16."""
+        return 64 if (self.device.type == "cuda" and self.d in (64, 128, 256)) else 16
+
+    def make_cache(self, num_blocks: int, block_size: int):
+        from ..engine.kv_cache import KVCache
+
+        return KVCache(self.spec.n_layers, num_blocks, block_size, self.hkv, self.d, self.dtype, self.device)
+
     # ------------------------------------------------------------------ weights
     def finalize(self):
         """Build the fused GPT-J style operands once all per-layer tensors are loaded."""

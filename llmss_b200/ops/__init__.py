@@ -14,8 +14,8 @@ from typing import Optional
 import torch
 
 from . import reference as ref
-from .reference import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_IDS, ACT_NONE, ACT_RELU, ACT_SILU, NORM_LAYER, NORM_RMS,
-                        ROPE_GPTJ, ROPE_NEOX, ROPE_NONE)
+from .reference import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_IDS, ACT_NONE, ACT_RELU, ACT_RELU2, ACT_SILU, NORM_DYT, NORM_LAYER,
+                        NORM_RMS, ROPE_GPTJ, ROPE_NEOX, ROPE_NONE)
 
 
 def _cuda(t: torch.Tensor) -> bool:
@@ -176,12 +176,95 @@ def _sdpa_prefill(qkv, out_view, batch, hq, hkv, d, scale, q_off, k_off, v_off):
         out_view[a:b] = o.transpose(1, 2).reshape(b - a, hq * d)
 
 
-def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0):
+def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, out_dtype=None):
+    """``out_dtype=torch.float32``: rows summed and stored in 32-bit (32-bit residual stream)."""
     if _cuda(wte):
         from . import cuda_impl as cu
 
+        if out_dtype == torch.float32:
+            return cu.embed_f32(tokens, wte, positions, wpe, pos_offset)
         return cu.embed(tokens, wte, positions, wpe, pos_offset)
-    return ref.embed(tokens, wte, positions, wpe, pos_offset)
+    return ref.embed(tokens, wte, positions, wpe, pos_offset, out_dtype=out_dtype)
+
+
+# ----------------------------------------------------------------------------- 32-bit residual stream, Dynamic Tanh
+def dyt_residual(resid, alpha: float, weight, bias, a=None, scale_a=None, b=None, scale_b=None, out_dtype=None,
+                 want_norm: bool = True):
+    """Fold up to two layer-scaled 32-bit branch outputs into the 32-bit residual and apply Dynamic Tanh
+    (tanh(alpha x) * weight + bias): returns (normed in ``out_dtype``, new residual).  ``want_norm=False`` only
+    updates the residual (before an op that is not a norm, e.g. a re-injection GEMM)."""
+    if _cuda(resid):
+        from . import cuda_impl as cu
+
+        return cu.dyt_residual(resid, alpha, weight, bias, a, scale_a, b, scale_b, out_dtype, want_norm)
+    return ref.dyt_residual(resid, alpha, weight, bias, a, scale_a, b, scale_b, out_dtype, want_norm)
+
+
+def cast_concat(a, b, dtype):
+    """[cast(a) | cast(b)] of two 32-bit [T, *] streams as one GEMM operand."""
+    if _cuda(a):
+        from . import cuda_impl as cu
+
+        return cu.cast_concat(a, b, dtype)
+    return ref.cast_concat(a, b, dtype)
+
+
+# ----------------------------------------------------------------------------- latent attention
+def latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapping, cache, dtype):
+    if _cuda(y):
+        from . import cuda_impl as cu
+
+        return cu.latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapping, cache, dtype)
+    return ref.latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapping, cache, dtype)
+
+
+def heads_matmul(x, w, heads, k, n, w_is_kn, row_scale=None, out_dtype=None):
+    if _cuda(x):
+        from . import cuda_impl as cu
+
+        return cu.heads_matmul(x, w, heads, k, n, w_is_kn, row_scale, out_dtype)
+    return ref.heads_matmul(x, w, heads, k, n, w_is_kn, row_scale, out_dtype)
+
+
+def latent_query_dtype(cache, heads, rank):
+    """Type in which latent_attention() wants the absorbed queries: the cache's 16-bit type where it will run on the
+    tcgen05 multi-query kernels, 32-bit for the generic kernel and on CPU."""
+    if _cuda(cache):
+        from . import cuda_impl as cu
+
+        if cu.latent_uses_tc(cache.dtype, rank, cache.shape[1], heads):
+            return cache.dtype
+    return torch.float32
+
+
+def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
+    """Causal attention of absorbed queries [T, heads * rank] over the paged latent cache (key = value = latent).
+
+    16-bit compute with a rank the tcgen05 multi-query kernels cover (64 / 128 / 256) runs on those (the latent
+    cache has their [blocks, 1, block_size, d] layout): decode batches on the split-KV decode kernel, portions of
+    prompts on the paged prefill kernel.  Every other case (true 32-bit, other ranks) runs the generic kernel."""
+    if _cuda(q_abs):
+        from . import cuda_impl as cu
+
+        return cu.latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype)
+    return ref.latent_attention(q_abs, cache, batch.block_tables, batch.seq_lens, batch.cu_q, heads, rank, scale, out_dtype)
+
+
+# ----------------------------------------------------------------------------- routed experts
+def moe_route(z, experts, top, groups, keep, route_scale):
+    if _cuda(z):
+        from . import cuda_impl as cu
+
+        return cu.moe_route(z, experts, top, groups, keep, route_scale)
+    return ref.moe_route(z, experts, top, groups, keep, route_scale)
+
+
+def moe_experts(h, ids, wts, w_up, w_down, act):
+    if _cuda(h):
+        from . import cuda_impl as cu
+
+        return cu.moe_experts(h, ids, wts, w_up, w_down, act)
+    return ref.moe_experts(h, ids, wts, w_up, w_down, act)
 
 
 def sample(logits, greedy, temperature, top_k, top_p, rng_state, vocab: Optional[int] = None, out=None):

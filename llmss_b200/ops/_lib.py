@@ -97,6 +97,24 @@ _SIGS = {
                             c_int64, c_int, c_void_p]),
     "llmss_sample": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p]),
+    "llmss_dyt_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_float, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "llmss_embed_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_int64, c_int, c_void_p]),
+    "llmss_cast_concat": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                                  c_void_p]),
+    "llmss_bgemm_simt": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64,
+                                 c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "llmss_latent_prep": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p,
+                                  c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+    "llmss_latent_attn_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
+    "llmss_latent_attn": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
+    "llmss_moe_route": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                                c_void_p]),
+    "llmss_moe_experts": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "llmss_moe_scale": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
 }
 _OPTIONAL = {
     "llmss_attn_prefill_paged": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,

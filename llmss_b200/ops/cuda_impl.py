@@ -83,7 +83,9 @@ def linear(x, w, bias=None, act: int = ACT_NONE, gated: bool = False, act_start:
     M, K, ldx = _rows2d(x)
     N, Kw, ldw = _rows2d(w)
     assert K == Kw, f"linear: x has K={K}, w has K={Kw}"
-    assert x.dtype == w.dtype and x.dtype in (torch.float16, torch.bfloat16)
+    assert x.dtype == w.dtype and x.dtype in _DT
+    if not (symm is not None and symm.nranks > 1) and _needs_simt(x, w, K, ldx, ldw):
+        return linear_simt(x, w, bias, act, gated, act_start, residual, out_dtype, out)
     out_f32 = 1 if out_dtype == torch.float32 else 0
     n_out = N // 2 if gated else N
     if out is None:
@@ -99,6 +101,33 @@ def linear(x, w, bias=None, act: int = ACT_NONE, gated: bool = False, act_start:
                            collective if ar else 0, None, _stream())
     _lib.check(rc, "llmss_gemm")
     _count()
+    return out
+
+
+def _needs_simt(x, w, K, ldx, ldw) -> bool:
+    """True 32-bit operands, or 16-bit ones that miss the 16-byte rules of the TMA operand loads."""
+    if x.dtype == torch.float32:
+        return True
+    return bool(K % 8 or ldx % 8 or ldw % 8 or x.data_ptr() % 16 or w.data_ptr() % 16)
+
+
+def linear_simt(x, w, bias=None, act: int = ACT_NONE, gated: bool = False, act_start: int = 0, residual=None,
+                out_dtype=None, out=None):
+    """The same linear layer on the CUDA cores (csrc/simt_gemm.cu): true 32-bit, or shapes the tcgen05 kernel refuses."""
+    if gated:
+        raise NotImplementedError("the CUDA-core GEMM has no gated epilogue")
+    lib = _lib.load()
+    M, K, ldx = _rows2d(x)
+    N, _, ldw = _rows2d(w)
+    f32 = x.dtype == torch.float32 or out_dtype == torch.float32
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if f32 else x.dtype, device=x.device)
+    rc = lib.llmss_bgemm_simt(_ptr(x), ldx, 0, _ptr(w), 0, 1, ldw, _ptr(bias), None, 0, _ptr(out), out.stride(0), 0, M, N, K, 1,
+                              act, act_start, _DT[x.dtype], 1 if f32 else 0, _stream())
+    _lib.check(rc, "llmss_bgemm_simt")
+    _count()
+    if residual is not None:
+        out += residual
     return out
 
 
@@ -371,3 +400,156 @@ def sample_vocab_parallel(local_logits, symm, vocab: int, greedy, temperature, t
     if cand_all is not None:
         vp_multinomial_merge(cand_all, symm.nranks, out)
     return out
+
+
+# --------------------------------------------------------------------------- 32-bit residual stream, Dynamic Tanh
+def embed_f32(tokens, wte, positions=None, wpe=None, pos_offset: int = 0):
+    lib = _lib.load()
+    T = tokens.numel()
+    V, H = wte.shape
+    out = torch.empty(T, H, dtype=torch.float32, device=wte.device)
+    rc = lib.llmss_embed_f32(_ptr(tokens), _ptr(positions), _ptr(wte), _ptr(wpe), _ptr(out), T, H, V,
+                             wpe.shape[0] if wpe is not None else 0, pos_offset, out.stride(0), _DT[wte.dtype], _stream())
+    _lib.check(rc, "llmss_embed_f32")
+    _count()
+    return out
+
+
+def dyt_residual(resid, alpha, weight, bias, a=None, scale_a=None, b=None, scale_b=None, out_dtype=None, want_norm=True):
+    lib = _lib.load()
+    M, H, ldr = _rows2d(resid)
+    assert resid.dtype == torch.float32 and all(t is None or t.dtype == torch.float32 for t in (a, b))
+    dt = out_dtype or weight.dtype
+    assert weight.dtype == dt, "dyt_residual: the norm weight has the compute type"
+    out = torch.empty(M, H, dtype=dt, device=resid.device) if want_norm else None
+    fold = a is not None or b is not None
+    new_res = torch.empty_like(resid) if fold else resid
+    rc = lib.llmss_dyt_residual(_ptr(resid), _ptr(new_res) if fold else None, _ptr(a), _ptr(scale_a), _ptr(b), _ptr(scale_b),
+                                _ptr(weight), _ptr(bias), _ptr(out), float(alpha), M, H, ldr,
+                                a.stride(0) if a is not None else 0, b.stride(0) if b is not None else 0,
+                                out.stride(0) if out is not None else 0, _DT[dt], _stream())
+    _lib.check(rc, "llmss_dyt_residual")
+    _count()
+    return out, new_res
+
+
+def cast_concat(a, b, dtype):
+    lib = _lib.load()
+    M, Ha, lda = _rows2d(a)
+    _, Hb, ldb = _rows2d(b)
+    out = torch.empty(M, Ha + Hb, dtype=dtype, device=a.device)
+    rc = lib.llmss_cast_concat(_ptr(a), _ptr(b), _ptr(out), M, Ha, Hb, lda, ldb, out.stride(0), _DT[dtype], _stream())
+    _lib.check(rc, "llmss_cast_concat")
+    _count()
+    return out
+
+
+# --------------------------------------------------------------------------- latent attention
+def latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapping, cache, dtype):
+    lib = _lib.load()
+    T, _, ldy = _rows2d(y)
+    assert y.dtype == torch.float32 and cache.dtype == dtype and cache.is_contiguous()
+    q = torch.empty(T, n_q, dtype=dtype, device=y.device)
+    gate = torch.empty(T, heads, dtype=torch.float32, device=y.device) if g_off >= 0 else None
+    rc = lib.llmss_latent_prep(_ptr(y), ldy, q_off, c_off, g_off, n_q, rank, heads, _ptr(norm_w), float(eps), _ptr(slot_mapping),
+                               _ptr(cache), _ptr(q), q.stride(0), _ptr(gate), T, _DT[dtype], _stream())
+    _lib.check(rc, "llmss_latent_prep")
+    _count()
+    return q, gate
+
+
+def heads_matmul(x, w, heads, k, n, w_is_kn, row_scale=None, out_dtype=None):
+    lib = _lib.load()
+    T, _, ldx = _rows2d(x)
+    assert x.dtype == w.dtype and w.is_contiguous()
+    f32 = x.dtype == torch.float32 or out_dtype == torch.float32
+    out = torch.empty(T, heads * n, dtype=torch.float32 if f32 else x.dtype, device=x.device)
+    swh, swk, swn = (k * n, n, 1) if w_is_kn else (n * k, 1, k)
+    rc = lib.llmss_bgemm_simt(_ptr(x), ldx, k, _ptr(w), swh, swk, swn, None, _ptr(row_scale),
+                              row_scale.stride(0) if row_scale is not None else 0, _ptr(out), out.stride(0), n, T, n, k, heads,
+                              ACT_NONE, 0, _DT[x.dtype], 1 if f32 else 0, _stream())
+    _lib.check(rc, "llmss_bgemm_simt(heads)")
+    _count()
+    return out
+
+
+_LATENT_TC = os.environ.get("LLMSS_LATENT_TC", "1") == "1"
+
+
+def latent_decode_splits(B: int, heads: int, max_kv: int) -> int:
+    """Key-range split of the generic latent kernel for decode: enough CTAs to cover the SMs, at least 256 keys each."""
+    ctas = B * -(-heads // 16)
+    return int(max(1, min(32, 296 // max(1, ctas), max_kv // 256)))
+
+
+def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
+    lib = _lib.load()
+    T = q_abs.shape[0]
+    bs = cache.shape[1]
+    dt = cache.dtype
+    out = torch.empty(T, heads * rank, dtype=out_dtype, device=q_abs.device)
+    if (_LATENT_TC and dt != torch.float32 and rank in (64, 128, 256) and bs in (16, 32, 64) and heads <= 128
+            and q_abs.dtype == dt and out_dtype == dt):
+        kv = cache.view(cache.shape[0], 1, bs, rank)       # one shared "KV head" that is key and value at once
+        if batch.is_decode:
+            splits = batch.decode_splits or decode_splits(batch.num_seqs, heads, 1, rank, batch.max_kv, dt, bs)
+            attn_decode(q_abs, kv, kv, batch.block_tables, batch.seq_lens, out, heads, 1, rank, scale, splits)
+            return out
+        if _lib.has("llmss_attn_prefill_paged"):
+            attn_prefill_paged(q_abs, kv, kv, batch.block_tables, batch.seq_lens, out, batch.cu_q, batch.num_seqs, batch.max_q,
+                               heads, 1, rank, scale)
+            return out
+    assert q_abs.dtype == torch.float32, "the generic latent kernel takes 32-bit absorbed queries"
+    splits = latent_decode_splits(batch.num_seqs, heads, batch.max_kv) if batch.is_decode else 1
+    scratch = None
+    if splits > 1:
+        scratch = arena(q_abs.device).attn_scratch(lib.llmss_latent_attn_scratch_floats(T, heads, rank, splits), q_abs.device)
+    rc = lib.llmss_latent_attn(_ptr(q_abs), q_abs.stride(0), _ptr(cache), _ptr(batch.block_tables), batch.block_tables.shape[1],
+                               bs, _ptr(batch.seq_lens), _ptr(batch.cu_q), _ptr(out), out.stride(0), _ptr(scratch), T,
+                               batch.num_seqs, batch.max_q, heads, rank, float(scale), splits, _DT[dt], _stream())
+    _lib.check(rc, "llmss_latent_attn")
+    _count(2 if splits > 1 else 1)
+    return out
+
+
+def latent_uses_tc(dtype, rank: int, block_size: int, heads: int) -> bool:
+    """Whether latent_attention() will run on the tcgen05 multi-query kernels (then it wants 16-bit absorbed queries)."""
+    return bool(_LATENT_TC and dtype != torch.float32 and rank in (64, 128, 256) and block_size in (16, 32, 64) and heads <= 128)
+
+
+# --------------------------------------------------------------------------- routed experts
+def moe_route(z, experts, top, groups, keep, route_scale, dense: bool = False):
+    lib = _lib.load()
+    T, _, ldz = _rows2d(z)
+    assert z.dtype == torch.float32
+    ids = torch.empty(T, top, dtype=torch.int32, device=z.device)
+    wts = torch.empty(T, top, dtype=torch.float32, device=z.device)
+    dn = torch.empty(T, experts, dtype=torch.float32, device=z.device) if dense else None
+    rc = lib.llmss_moe_route(_ptr(z), ldz, T, experts, top, groups, keep, float(route_scale), _ptr(ids), _ptr(wts), _ptr(dn),
+                             _stream())
+    _lib.check(rc, "llmss_moe_route")
+    _count()
+    return (ids, wts, dn) if dense else (ids, wts)
+
+
+def moe_experts(h, ids, wts, w_up, w_down, act):
+    lib = _lib.load()
+    T, W, ldh = _rows2d(h)
+    E, F, _ = w_up.shape
+    top = ids.shape[1]
+    assert w_up.is_contiguous() and w_down.is_contiguous() and h.dtype == w_up.dtype
+    scratch = torch.empty(T, top, F, dtype=h.dtype, device=h.device)
+    out = torch.empty(T, W, dtype=torch.float32, device=h.device)
+    rc = lib.llmss_moe_experts(_ptr(h), ldh, _ptr(ids), _ptr(wts), _ptr(w_up), _ptr(w_down), w_down.stride(0), _ptr(scratch), _ptr(out),
+                               out.stride(0), T, W, F, top, act, _DT[h.dtype], _stream())
+    _lib.check(rc, "llmss_moe_experts")
+    _count(2)
+    return out
+
+
+def moe_scale(a, dense, experts: int, ff: int):
+    lib = _lib.load()
+    rc = lib.llmss_moe_scale(_ptr(a), a.stride(0), _ptr(dense), a.shape[0], experts, ff, _DT[a.dtype], _stream())
+    _lib.check(rc, "llmss_moe_scale")
+    _count()
+    return a

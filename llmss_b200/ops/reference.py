@@ -13,13 +13,13 @@ from typing import Optional, Tuple
 import torch
 import torch.nn.functional as F
 
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU = 0, 1, 2, 3, 4
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_RELU2 = 0, 1, 2, 3, 4, 5
 ACT_IDS = {
     None: ACT_NONE, "none": ACT_NONE,
     "gelu_new": ACT_GELU_TANH, "gelu_pytorch_tanh": ACT_GELU_TANH, "gelu_fast": ACT_GELU_TANH,
-    "gelu": ACT_GELU_ERF, "relu": ACT_RELU, "silu": ACT_SILU, "swish": ACT_SILU,
+    "gelu": ACT_GELU_ERF, "relu": ACT_RELU, "silu": ACT_SILU, "swish": ACT_SILU, "relu2": ACT_RELU2,
 }
-NORM_LAYER, NORM_RMS = 0, 1
+NORM_LAYER, NORM_RMS, NORM_DYT = 0, 1, 2
 ROPE_NONE, ROPE_GPTJ, ROPE_NEOX = 0, 1, 2
 
 
@@ -34,6 +34,8 @@ def apply_act(x: torch.Tensor, act: int) -> torch.Tensor:
         return F.relu(x)
     if act == ACT_SILU:
         return F.silu(x)
+    if act == ACT_RELU2:
+        return F.relu(x).square()
     raise ValueError(act)
 
 
@@ -155,11 +157,111 @@ def attention_paged(q, k_cache, v_cache, block_tables, seq_lens, cu_q, scale: fl
 
 
 def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, out_dtype=None):
-    """Token (+ learned position) embedding (G1; replicated tables, no collective)."""
-    h = F.embedding(tokens.long(), wte)
+    """Token (+ learned position) embedding (G1; replicated tables, no collective).  With a 32-bit ``out_dtype``
+    the two rows are summed in 32-bit (models that keep their residual stream in 32-bit)."""
+    od = out_dtype or wte.dtype
+    up = torch.float32 if od == torch.float32 else wte.dtype
+    h = F.embedding(tokens.long(), wte).to(up)
     if wpe is not None:
-        h = h + F.embedding(positions.long() + pos_offset, wpe)
-    return h.to(out_dtype or wte.dtype)
+        h = h + F.embedding(positions.long() + pos_offset, wpe).to(up)
+    return h.to(od)
+
+
+# ----------------------------------------------------------------------------- 32-bit residual + Dynamic Tanh
+def dyt_residual(resid, alpha: float, weight, bias, a=None, scale_a=None, b=None, scale_b=None, out_dtype=None,
+                 want_norm: bool = True):
+    """r' = r + scale_a * a + scale_b * b (all 32-bit);  returns (tanh(alpha r') * weight + bias in out_dtype, r')."""
+    r = resid.float()
+    for br, sc in ((a, scale_a), (b, scale_b)):
+        if br is not None:
+            r = r + (br.float() if sc is None else sc.float() * br.float())
+    if not want_norm:
+        return None, r
+    y = torch.tanh(alpha * r) * weight.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype or weight.dtype), r
+
+
+def cast_concat(a, b, dtype):
+    return torch.cat([a, b], dim=-1).to(dtype)
+
+
+# ----------------------------------------------------------------------------- latent attention
+def latent_prep(y, q_off: int, c_off: int, g_off: int, n_q: int, rank: int, heads: int, norm_w, eps: float,
+                slot_mapping, cache, dtype):
+    """y: [T, *] 32-bit fused projection.  RMS-norms the latent columns and writes them to the paged cache
+    ([num_blocks, block_size, rank]); returns (q in `dtype`, sigmoid(gate columns) [T, heads] or None)."""
+    c = y[:, c_off:c_off + rank].float()
+    c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+    valid = slot_mapping >= 0
+    flat = cache.view(-1, rank)
+    flat[slot_mapping[valid].long()] = c[valid].to(cache.dtype)
+    q = y[:, q_off:q_off + n_q].to(dtype)
+    gate = torch.sigmoid(y[:, g_off:g_off + heads].float()) if g_off >= 0 else None
+    return q, gate
+
+
+def heads_matmul(x, w, heads: int, k: int, n: int, w_is_kn: bool, row_scale=None, out_dtype=None):
+    """Per-head product.  x: [T, heads * k]; w: [heads * k, n] (``w_is_kn``: rows index (head, k)) or [heads * n, k]
+    (rows index (head, n)).  Returns [T, heads * n], optionally scaled per (token, head) by row_scale [T, heads]."""
+    T = x.shape[0]
+    xh = x.float().view(T, heads, k)
+    wh = w.float().view(heads, k, n) if w_is_kn else w.float().view(heads, n, k).transpose(1, 2)
+    o = torch.einsum("thk,hkn->thn", xh, wh)
+    if row_scale is not None:
+        o = o * row_scale.float()[:, :, None]
+    return o.reshape(T, heads * n).to(out_dtype or x.dtype)
+
+
+def latent_attention(q_abs, cache, block_tables, seq_lens, cu_q, heads: int, rank: int, scale: float, out_dtype=None):
+    """Absorbed latent attention: the cached latent is key and value of every head (see csrc/latent_attn.cu).
+    q_abs: [T, heads * rank]; cache: [num_blocks, block_size, rank].  Returns [T, heads * rank]."""
+    T = q_abs.shape[0]
+    bs = cache.shape[1]
+    out = torch.zeros(T, heads, rank, dtype=torch.float32, device=q_abs.device)
+    cu, lens = cu_q.tolist(), seq_lens.tolist()
+    for i, L in enumerate(lens):
+        q0, q1 = cu[i], cu[i + 1]
+        ql = q1 - q0
+        if ql == 0 or L == 0:
+            continue
+        nb = (L + bs - 1) // bs
+        c = cache[block_tables[i, :nb].long()].reshape(nb * bs, rank)[:L].float()
+        qi = q_abs[q0:q1].float().view(ql, heads, rank)
+        s = torch.einsum("thr,jr->htj", qi, c) * scale
+        qpos = torch.arange(L - ql, L, device=c.device)[:, None]
+        kpos = torch.arange(L, device=c.device)[None, :]
+        s = s.masked_fill(kpos > qpos, float("-inf"))
+        out[q0:q1] = torch.einsum("htj,jr->thr", torch.softmax(s, dim=-1), c)
+    return out.reshape(T, heads * rank).to(out_dtype or q_abs.dtype)
+
+
+# ----------------------------------------------------------------------------- routed experts
+def moe_route(z, experts: int, top: int, groups: int, keep: int, route_scale: float):
+    """Group-limited top-k routing on 32-bit logits z [T, experts] -> (ids [T, top] int32, weights [T, top] fp32).
+    Ties go to the lower index (stable sort), like the CUDA kernel."""
+    s = torch.softmax(z.float(), dim=-1)
+    T = s.shape[0]
+    gs = s.view(T, groups, experts // groups).amax(-1)
+    best = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :keep]
+    allow = torch.zeros(T, groups, dtype=torch.bool, device=z.device).scatter_(1, best, True)
+    allow = allow[:, :, None].expand(T, groups, experts // groups).reshape(T, experts)
+    idx = torch.sort(s.masked_fill(~allow, -1.0), dim=-1, descending=True, stable=True).indices[:, :top]
+    w = s.gather(1, idx)
+    w = w / (w.sum(-1, keepdim=True) + 1e-20) * route_scale
+    return idx.to(torch.int32), w
+
+
+def moe_experts(h, ids, wts, w_up, w_down, act: int):
+    """out[t] = sum_k wts[t, k] * W_down[ids[t, k]] act(W_up[ids[t, k]] h[t]);  w_up [E, F, W]; w_down [W, E * F] (the
+    experts' down matrices side by side); fp32 result."""
+    T, W = h.shape
+    E, F, _ = w_up.shape
+    up = w_up.float()[ids.long()]                       # [T, top, F, W]
+    a = apply_act(torch.einsum("tkfw,tw->tkf", up, h.float()), act).to(h.dtype).float()
+    down = w_down.float().view(W, E, F).permute(1, 0, 2)[ids.long()]   # [T, top, W, F]
+    return torch.einsum("tkwf,tkf,tk->tw", down, a, wts.float())
 
 
 def _fmix32(x):
