@@ -61,10 +61,84 @@ PRESETS: Dict[str, dict] = {
 }
 
 
+def bedovik_config(width: int, vocab: int, max_positions: int, layers, loop=None, eps: float = 1e-5) -> dict:
+    """config.json of a Bedovik model.  ``layers``: one dict per layer with keys gated (bool), heads, dim, vdim, kv_rank
+    and optionally scale, experts, top, groups, keep, route_scale, ff (no ``experts``: a layer without feed-forward).
+    ``loop``: (start, stop, times) or None."""
+    out = []
+    for L in layers:
+        mlp = None
+        if L.get("experts"):
+            mlp = {"kind": "moe", "expert": {"ff": L["ff"]},
+                   "router": {"experts": L["experts"], "top": L["top"], "scale": L.get("route_scale", 1.0),
+                              "groups": {"count": L.get("groups", 1), "keep": L.get("keep", L.get("groups", 1))}}}
+        out.append({"type": "latent_attention" if L.get("gated", True) else "latent_attention_2",
+                    "mixer": {"heads": L["heads"], "dim": L["dim"], "vdim": L["vdim"], "kv_rank": L["kv_rank"],
+                              "scale": L.get("scale", L["dim"] ** -0.5)},
+                    "mlp": mlp})
+    cfg = {"architecture": "Bedovik", "vocab": vocab, "width": width, "max_positions": max_positions, "norm": {"eps": eps},
+           "layers": out}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def _bedovik_shapes(cfg: dict):
+    W, V, P = cfg["width"], cfg["vocab"], cfg["max_positions"]
+    yield "embed", (V, W), "unit"
+    yield "pos", (P, W), "emb"
+    if cfg.get("loop"):
+        yield "loop.in", (W, 2 * W), "fan"
+        yield "loop.step", (cfg["loop"]["times"], W), "b"
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}", L["mixer"]
+        H, d, dv, R = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+        yield f"{p}.norm1", (W,), "ln_w"
+        yield f"{p}.norm1.b", (W,), "ln_b"
+        yield f"{p}.norm1.alpha", (), "alpha"
+        yield f"{p}.mix.q", (H * d, W), "fan"
+        yield f"{p}.mix.dkv", (R, W), "fan"
+        yield f"{p}.mix.dkv.norm", (R,), "ln_w"
+        yield f"{p}.mix.uk", (H * d, R), "fan"
+        yield f"{p}.mix.uv", (H * dv, R), "fan"
+        if L["type"] == "latent_attention":
+            yield f"{p}.mix.g", (H, W), "fan"
+        yield f"{p}.mix.o", (W, H * dv), "fan"
+        yield f"{p}.ls1", (W,), "ls"
+        if L.get("mlp"):
+            F, E = L["mlp"]["expert"]["ff"], L["mlp"]["router"]["experts"]
+            for e in range(E):
+                yield f"{p}.mlp.e{e}.up", (F, W), "fan"
+                yield f"{p}.mlp.e{e}.down", (W, F), "fan"
+            yield f"{p}.mlp.router", (E, W), "fan2"
+            yield f"{p}.ls2", (W,), "ls"
+    yield "final.norm", (W,), "ln_w"
+    yield "final.norm.b", (W,), "ln_b"
+    yield "final.norm.alpha", (), "alpha"
+    yield "head", (V, W), "fan"
+
+
+def _bedovik_preset(width, vocab, heads, dim, vdim, rank, experts, top, groups, keep, ff, n_layers, loop, max_positions=4096):
+    layers = [dict(gated=(i % 2 == 0), heads=heads, dim=dim, vdim=vdim, kv_rank=rank, experts=experts, top=top, groups=groups,
+                   keep=keep, route_scale=2.0, ff=ff) for i in range(n_layers)]
+    return bedovik_config(width, vocab, max_positions, layers, loop)
+
+
+PRESETS.update({
+    # latent attention + routed experts at sizes whose layers resemble a served model's (random weights)
+    "bedovik-tiny": _bedovik_preset(128, 320, 4, 16, 24, 64, 8, 2, 4, 2, 32, 3, (1, 3, 2), 256),
+    "bedovik-2b": _bedovik_preset(2048, 32000, 16, 128, 128, 256, 32, 4, 8, 4, 1024, 12, (2, 10, 2)),
+    "bedovik-7b": _bedovik_preset(4096, 32000, 32, 128, 128, 256, 64, 6, 8, 4, 1408, 16, (2, 14, 2)),
+})
+
+
 def _shapes(cfg: dict) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
-    """(name, shape, kind) for every tensor of the family; kind in {w, b, ln_w, ln_b, emb}."""
-    mt = cfg["model_type"]
-    if mt == "gptj":
+    """(name, shape, kind) for every tensor of the family; kind in {w, b, ln_w, ln_b, emb} (and, for architectures whose
+    activations must keep unit scale without trained weights: unit, fan, fan2, alpha, ls)."""
+    mt = cfg.get("model_type") or str(cfg["architecture"]).lower()
+    if mt == "bedovik":
+        yield from _bedovik_shapes(cfg)
+    elif mt == "gptj":
         H, L, V = cfg["n_embd"], cfg["n_layer"], cfg["vocab_size"]
         F = cfg.get("n_inner") or 4 * H
         yield "transformer.wte.weight", (V, H), "emb"
@@ -205,7 +279,11 @@ def write_random_checkpoint(path, preset_or_cfg, dtype=torch.float16, device=Non
             shard, size = {}, 0
 
     for name, shape, kind in _shapes(cfg):
-        if kind == "ln_w":
+        if kind in ("unit", "fan", "fan2", "alpha", "ls"):
+            r = torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
+            t = {"unit": r, "fan": r * shape[-1] ** -0.5 if shape else r, "fan2": 2.0 * r * shape[-1] ** -0.5 if shape else r,
+                 "alpha": 0.7 + 0.1 * r, "ls": 0.4 + 0.1 * r}[kind]
+        elif kind == "ln_w":
             t = 1.0 + 0.05 * torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
         elif kind in ("b", "ln_b"):
             t = 0.02 * torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
