@@ -779,6 +779,17 @@ LLMSS_API int llmss_attn_decode_tc_pick_splits(int B, int hkv, int d, int max_kv
   return best;
 }
 
+// Whether llmss_attn_decode_tc can take this head grouping and head size (its query tile and at least two key stages must
+// fit into shared memory): callers with an alternative kernel ask first instead of catching the refusal.
+LLMSS_API int llmss_attn_decode_tc_supported(int hq, int hkv, int d, int block_size) {
+  if (!(d == 64 || d == 128 || d == 256) || hq <= 0 || hkv <= 0 || hq % hkv != 0 || hq / hkv > 128) return 0;
+  if (!(block_size == 16 || block_size == 32 || block_size == 64)) return 0;
+  const int G = hq / hkv;
+  const int q_alloc_rows = G <= 8 ? 8 : (G <= 64 ? 128 : (G + 7) / 8 * 8);
+  int smem = 0;
+  return plan_stages(q_alloc_rows, d, &smem) >= 2 ? 1 : 0;
+}
+
 // Tensor-core (tcgen05) paged decode attention: the q heads of a KV group are MMA rows.  Same contract
 // as llmss_attn_decode; `scratch` holds the split-KV partials.  Requires block_size in {16, 32, 64}, head_dim in
 // {64, 128, 256}, hq / hkv <= 128.

@@ -188,12 +188,8 @@ class BedovikLM(nn.Module):
                 h, x = ops.dyt_residual(x, L.alpha, L.norm_w, L.norm_b, *pend, out_dtype=dt)
             with trace("gemm_in"):
                 y = ops.linear(h, L.w_in, out_dtype=torch.float32)
-            with trace("mixer"):
-                a = L.mixer.forward(y, batch, kv.latent(run), dt)
-            m = None
-            if L.ffn is not None:
-                with trace("experts"):
-                    m = L.ffn.forward(h, y)
+            a = L.mixer.forward(y, batch, kv.latent(run), dt)
+            m = L.ffn.forward(h, y) if L.ffn is not None else None
             pend = (a, L.ls1, m, L.ls2)
             if taps is not None:
                 taps.append(ops.dyt_residual(x, 1.0, L.norm_w, None, *pend, out_dtype=dt, want_norm=False)[1].clone())

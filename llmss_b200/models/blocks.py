@@ -14,6 +14,7 @@ import torch
 
 from .. import ops
 from ..ops import ACT_RELU2
+from ..utils.tracing import trace
 
 
 class LatentAttention:
@@ -46,24 +47,31 @@ class LatentAttention:
     def forward(self, y, batch, cache, dtype):
         """y: the layer's fused 32-bit projection [T, *]; returns the block's 32-bit output [T, width]."""
         H, R = self.heads, self.rank
-        q, gate = ops.latent_prep(y, self.q_off, self.c_off, self.g_off, H * self.dim, R, H, self.norm_w, self.eps,
-                                  batch.slot_mapping, cache, dtype)
-        q_abs = ops.heads_matmul(q, self.w_uk, H, self.dim, R, True, out_dtype=ops.latent_query_dtype(cache, H, R))
-        o_lat = ops.latent_attention(q_abs, cache, batch, H, R, self.scale, dtype)
-        ctx = ops.heads_matmul(o_lat, self.w_uv, H, R, self.vdim, False, row_scale=gate, out_dtype=dtype)
-        return ops.linear(ctx, self.w_o, out_dtype=torch.float32)
+        with trace("latent_prep"):
+            q, gate = ops.latent_prep(y, self.q_off, self.c_off, self.g_off, H * self.dim, R, H, self.norm_w, self.eps,
+                                      batch.slot_mapping, cache, dtype)
+        with trace("latent_absorb"):
+            q_abs = ops.heads_matmul(q, self.w_uk, H, self.dim, R, True, out_dtype=ops.latent_query_dtype(cache, H, R))
+        with trace("latent_attention"):
+            o_lat = ops.latent_attention(q_abs, cache, batch, H, R, self.scale, dtype)
+        with trace("latent_unabsorb"):
+            ctx = ops.heads_matmul(o_lat, self.w_uv, H, R, self.vdim, False, row_scale=gate, out_dtype=dtype)
+        with trace("gemm_out"):
+            return ops.linear(ctx, self.w_o, out_dtype=torch.float32)
 
 
-_DENSE_MIN = int(os.environ.get("LLMSS_MOE_DENSE_MIN_TOKENS", "256"))
+_DENSE_MIN = int(os.environ.get("LLMSS_MOE_DENSE_MIN_TOKENS", "0"))   # 0: dense as soon as token x top pairs >= experts
 
 
 class RoutedExperts:
     """Mixture of small feed-forward experts with group-limited top-k routing (csrc/moe.cu).
 
-    Router logits come from the layer's fused input projection (32-bit accumulation).  Short batches gather the
-    chosen experts' weight rows per token; from ``LLMSS_MOE_DENSE_MIN_TOKENS`` tokens on, 16-bit CUDA batches run the
-    dense form: every expert's up-projection in one tensor-core GEMM (activation fused), each expert's block scaled
-    by its routing weight (0 if not chosen), one GEMM over the side-by-side down matrices."""
+    Router logits come from the layer's fused input projection (32-bit accumulation).  A batch with fewer (token,
+    chosen expert) pairs than experts gathers the chosen experts' weight rows per token -- it reads only those bytes.
+    From there on a batch touches about every expert anyway, and 16-bit CUDA batches run the dense form: every expert's
+    up-projection in one tensor-core GEMM (activation fused) that streams each weight once, each expert's block
+    scaled by its routing weight (0 if not chosen), one GEMM over the side-by-side down matrices.  The dense form
+    spends experts / top times the needed FLOPs; ``LLMSS_MOE_DENSE_MIN_TOKENS`` moves the switch."""
 
     def __init__(self, experts: int, top: int, groups: int, keep: int, route_scale: float, ff: int, act: int = ACT_RELU2):
         if experts % groups or not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
@@ -83,12 +91,17 @@ class RoutedExperts:
         E, F = self.experts, self.ff
         z = y[:, self.z_off:self.z_off + E]
         T = h.shape[0]
-        if h.is_cuda and h.dtype != torch.float32 and T >= _DENSE_MIN:
+        if h.is_cuda and h.dtype != torch.float32 and T >= (_DENSE_MIN or -(-E // self.top)):
             from ..ops import cuda_impl as cu
 
-            _, _, dense = cu.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale, dense=True)
-            a = ops.linear(h, self.w_up.view(E * F, -1), act=self.act)
-            cu.moe_scale(a, dense, E, F)
-            return ops.linear(a, self.w_down, out_dtype=torch.float32)
-        ids, wts = ops.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale)
-        return ops.moe_experts(h, ids, wts, self.w_up, self.w_down, self.act)
+            with trace("experts_route"):
+                _, _, dense = cu.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale, dense=True)
+            with trace("experts_dense_up"):
+                a = ops.linear(h, self.w_up.view(E * F, -1), act=self.act)
+                cu.moe_scale(a, dense, E, F)
+            with trace("experts_dense_down"):
+                return ops.linear(a, self.w_down, out_dtype=torch.float32)
+        with trace("experts_route"):
+            ids, wts = ops.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale)
+        with trace("experts_gather"):
+            return ops.moe_experts(h, ids, wts, self.w_up, self.w_down, self.act)

@@ -488,8 +488,7 @@ def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
     bs = cache.shape[1]
     dt = cache.dtype
     out = torch.empty(T, heads * rank, dtype=out_dtype, device=q_abs.device)
-    if (_LATENT_TC and dt != torch.float32 and rank in (64, 128, 256) and bs in (16, 32, 64) and heads <= 128
-            and q_abs.dtype == dt and out_dtype == dt):
+    if latent_uses_tc(dt, rank, bs, heads) and q_abs.dtype == dt and out_dtype == dt:
         kv = cache.view(cache.shape[0], 1, bs, rank)       # one shared "KV head" that is key and value at once
         if batch.is_decode:
             splits = batch.decode_splits or decode_splits(batch.num_seqs, heads, 1, rank, batch.max_kv, dt, bs)
@@ -514,7 +513,11 @@ def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
 
 def latent_uses_tc(dtype, rank: int, block_size: int, heads: int) -> bool:
     """Whether latent_attention() will run on the tcgen05 multi-query kernels (then it wants 16-bit absorbed queries)."""
-    return bool(_LATENT_TC and dtype != torch.float32 and rank in (64, 128, 256) and block_size in (16, 32, 64) and heads <= 128)
+    if not (_LATENT_TC and dtype != torch.float32 and rank in (64, 128, 256) and block_size in (16, 32, 64) and heads <= 128):
+        return False
+    # all heads form one query group over the single latent "KV head": the decode kernel must be able to hold that tile
+    return not use_tc_decode(heads, 1, rank, block_size) or bool(
+        _lib.load().llmss_attn_decode_tc_supported(heads, 1, rank, block_size))
 
 
 # --------------------------------------------------------------------------- routed experts

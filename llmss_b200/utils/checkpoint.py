@@ -125,10 +125,17 @@ def _bedovik_preset(width, vocab, heads, dim, vdim, rank, experts, top, groups, 
 
 
 PRESETS.update({
-    # latent attention + routed experts at sizes whose layers resemble a served model's (random weights)
+    # latent attention + routed experts at sizes whose layers resemble a served model's (random weights); the
+    # gptj-like-* presets are multi-head models of equal width, depth (= layer runs), heads and active feed-forward size
     "bedovik-tiny": _bedovik_preset(128, 320, 4, 16, 24, 64, 8, 2, 4, 2, 32, 3, (1, 3, 2), 256),
-    "bedovik-2b": _bedovik_preset(2048, 32000, 16, 128, 128, 256, 32, 4, 8, 4, 1024, 12, (2, 10, 2)),
-    "bedovik-7b": _bedovik_preset(4096, 32000, 32, 128, 128, 256, 64, 6, 8, 4, 1408, 16, (2, 14, 2)),
+    "bedovik-2k": _bedovik_preset(2048, 32000, 16, 128, 128, 128, 16, 4, 4, 2, 1024, 10, (1, 9, 2)),
+    "bedovik-4k": _bedovik_preset(4096, 32000, 32, 128, 128, 128, 32, 4, 8, 4, 1536, 10, (1, 9, 2)),
+    "gptj-like-2k": dict(model_type="gptj", architectures=["GPTJForCausalLM"], vocab_size=32000, n_positions=4096, n_embd=2048,
+                         n_layer=18, n_head=16, rotary_dim=64, n_inner=4096, activation_function="gelu_new",
+                         layer_norm_epsilon=1e-5, tie_word_embeddings=False, bos_token_id=0, eos_token_id=0),
+    "gptj-like-4k": dict(model_type="gptj", architectures=["GPTJForCausalLM"], vocab_size=32000, n_positions=4096, n_embd=4096,
+                         n_layer=18, n_head=32, rotary_dim=64, n_inner=6144, activation_function="gelu_new",
+                         layer_norm_epsilon=1e-5, tie_word_embeddings=False, bos_token_id=0, eos_token_id=0),
 })
 
 

@@ -49,11 +49,17 @@ def tokens_for(cfg, n, seed):
     return torch.randint(0, cfg["vocab"], (n,), generator=g).tolist()
 
 
-def close(got, want, tol):
-    """Largest difference relative to the spread of the expected logits."""
-    got, want = got.double().cpu(), want.double()
-    err = (got - want).abs().max().item() / max(want.std().item(), 1e-6)
-    assert err < tol, f"relative error {err:.3g} >= {tol}"
+def close(got, want, tol, rows_over=0.0):
+    """Largest difference, and root mean square difference, relative to the spread of the expected values.  `rows_over`: share
+    of rows that may exceed `tol` (up to 4 x): 16-bit runs flip a routing decision now and then where two expert scores
+    nearly tie, which moves that one position; the true 32-bit runs allow none."""
+    got, want = got.double().cpu(), want.double().cpu()
+    spread = max(want.std().item(), 1e-6)
+    d = (got - want).abs().reshape(got.shape[0], -1).max(-1).values / spread
+    rms = (got - want).pow(2).mean().sqrt().item() / spread
+    over = (d >= tol).sum().item()
+    assert over <= rows_over * d.numel() and d.max().item() < (4 * tol if rows_over else tol) and rms < tol / 4, \
+        f"relative error max {d.max().item():.3g} rms {rms:.3g}, {over} of {d.numel()} rows over {tol}"
 
 
 def feed_in_portions(eng, key, toks, sizes):
