@@ -52,6 +52,9 @@ def parse():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--block-size", type=int, default=None, help="KV page size (default: engine's choice, 64 on CUDA)")
     ap.add_argument("--profile-ops", action="store_true", help="eager decode with per-op CUDA-event timing (diagnostic)")
+    ap.add_argument("--compare", default=None, metavar="A:B[,A:B...]",
+                    help="instead of the headline run: prefill and decode tokens/s plus per-op device times of preset A beside "
+                         "preset B (e.g. bedovik-2k:gptj-like-2k,bedovik-4k:gptj-like-4k), one JSON line per preset")
     return ap.parse_args()
 
 
@@ -296,9 +299,10 @@ def run_ours(args, rank, world, local):
         "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "fp16", "data": "synthetic",
         "impl": "ours",
         "config": bench_config(args, world),
-        "details": {"cuda_graph": not args.no_graph, "fused_parallel_block": eng.core.fuse_parallel,
+        "details": {"cuda_graph": not args.no_graph, "fused_parallel_block": getattr(eng.core, "fuse_parallel", None),
                     "symmetric_heap": getattr(eng.comm.symm, "mode", None), "nvls_multicast": bool(getattr(eng.comm.symm, "has_multicast", False)),
-                    "heads_per_rank": eng.core.hq, "padded_heads": eng.core.heads_padded - eng.core.spec.n_heads},
+                    "heads_per_rank": getattr(eng.core, "hq", None),
+                    "padded_heads": (eng.core.heads_padded - eng.core.spec.n_heads) if hasattr(eng.core, "heads_padded") else 0},
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": round(1e3 * e2e_s / K, 4)},
@@ -310,6 +314,97 @@ def run_ours(args, rank, world, local):
     }
     if rank == 0:
         print(json.dumps(out), flush=True)
+
+
+# ----------------------------------------------------------------------------- architecture comparison
+def run_compare(args, rank, world, local):
+    """Prefill and decode throughput of two presets side by side (one GPU), with the per-op device times of one packed prefill
+    round and of one decode step (eager, CUDA events per op) so that like kernels can be set against their rooflines.
+    Same timing rules as the headline run: warm-up, weights + cache streamed each step (larger than L2), CUDA events."""
+    from llmss_b200.engine.engine import Engine
+    from llmss_b200.engine.runner import SamplingParams
+    from llmss_b200.ops import _lib
+    from llmss_b200.utils import tracing
+    from llmss_b200.utils.dist import initialize_torch_distributed
+
+    assert world == 1, "--compare runs on one GPU"
+    pg, _, _ = initialize_torch_distributed(timeout_s=600)
+    K, Wm, B, S = args.steps, args.warmup, args.batch, args.prompt_len
+    total_new = 1 + K + Wm + 8 + 4
+    for preset in [m for pair in args.compare.split(",") for m in pair.split(":")]:
+        args.model = preset
+        path = ensure_checkpoint(args, rank, world)
+        eng = Engine.from_pretrained(path, dtype=torch.bfloat16, device=torch.device("cuda", local), process_group=pg, max_batch=B,
+                                     max_seq_len=S + total_new + 16, use_cuda_graph=not args.no_graph, max_prefill_tokens=8192,
+                                     block_size=args.block_size)
+        runner = eng.runner
+        prompts = synthetic_prompts(B, S, eng.core.spec.vocab)
+        sp = SamplingParams(max_new_tokens=total_new, is_greedy=True)
+        # warm the prefill kernels on one round's worth of prompts, then give the pages back
+        warm = eng.generate(prompts[:max(1, 8192 // S)], SamplingParams(max_new_tokens=1, is_greedy=True))
+        assert len(warm) > 0
+        for p in prompts:
+            eng.add_request(p, sp)
+        fence(world)
+        sampler = ClockSampler(local)
+        sampler.start()
+        n0 = _lib.LAUNCHES["count"]
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        while eng.waiting:
+            eng.step()
+        ev1.record()
+        fence(world)
+        prefill_ms = ev0.elapsed_time(ev1)
+        prefill_launches = _lib.LAUNCHES["count"] - n0
+        eng.step()                      # binds the batch, captures the decode graph
+        for _ in range(Wm):
+            runner.decode_step(sync=False, host_tokens=False)
+        fence(world)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(K):
+            runner.decode_step(sync=False, host_tokens=False)
+        ev1.record()
+        fence(world)
+        clocks = sampler.stop()
+        decode_ms = ev0.elapsed_time(ev1) / K
+        runner.sync_lengths()
+        # per-op device time: one eager decode step, then one packed prefill round through the same step function
+        tracing.enable(profile=True)
+        tracing.reset()
+        graph, runner.use_graph = runner.use_graph, False
+        for _ in range(3):
+            runner.decode_step(sync=False, host_tokens=False)
+        dec_ops = {k: round(v["total_us"] / 3, 1) for k, v in tracing.report().items()}
+        dec_calls = {k: v["calls"] // 3 for k, v in tracing.report().items()}
+        runner.sync_lengths()
+        runner.use_graph = graph
+        eng.abort_all()
+        n_pf = max(1, 8192 // S)
+        eng.generate(prompts[:n_pf], SamplingParams(max_new_tokens=1, is_greedy=True))   # the allocator settles
+        tracing.reset()
+        eng.generate(prompts[:n_pf], SamplingParams(max_new_tokens=1, is_greedy=True))
+        pf_ops = {k: v["total_us"] for k, v in tracing.report().items()}
+        pf_calls = {k: v["calls"] for k, v in tracing.report().items()}
+        tracing.enable(profile=False)
+        out = {"impl": "ours", "compare": preset, "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+               "config": {"model": f"{preset} (random-init)", "global_batch": B, "prompt_len": S, "steps": K, "warmup": Wm,
+                          "l2": "inputs larger than L2 (weights + cache streamed each step)"},
+               "params_local": int(eng.core.num_parameters_local()),
+               "prefill_tokens_per_s": round(B * S / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 2),
+               "prefill_launches": int(prefill_launches),
+               "decode_tokens_per_s": round(B / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+               "decode_ctx": S, "decode_launches_per_step": int(runner.launches_per_graph.get(runner._bucket(B), 0)),
+               "decode_ops_us_per_step": dec_ops, "decode_op_calls_per_step": dec_calls,
+               "prefill_round_tokens": n_pf * S, "prefill_ops_us_per_round": pf_ops, "prefill_op_calls_per_round": pf_calls,
+               "clocks": clocks}
+        print(json.dumps(out), flush=True)
+        del eng, runner
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
 
 
 # ----------------------------------------------------------------------------- reference arm
@@ -410,7 +505,9 @@ def main():
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
         return
     rank, world, local = dist_setup(args.gpus)
-    if args.impl == "reference":
+    if args.compare:
+        run_compare(args, rank, world, local)
+    elif args.impl == "reference":
         run_reference(args, rank, world, local)
     else:
         run_ours(args, rank, world, local)

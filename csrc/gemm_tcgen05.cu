@@ -202,6 +202,7 @@ __device__ __forceinline__ float act_t(float x, int runtime_act) {
   if constexpr (ACT == LLMSS_ACT_NONE) return x;
   else if constexpr (ACT == LLMSS_ACT_GELU_TANH) return 0.5f * x * (1.0f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
   else if constexpr (ACT == LLMSS_ACT_SILU) return __fdividef(x, 1.0f + __expf(-x));
+  else if constexpr (ACT == LLMSS_ACT_RELU2) { const float r = fmaxf(x, 0.0f); return r * r; }
   else return act_fast(x, runtime_act);
 }
 
@@ -252,6 +253,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const float (&v)[
   } else if (a.epi == EPI_ACT) {
     if (a.act == LLMSS_ACT_GELU_TANH) LLMSS_SC(EPI_ACT, LLMSS_ACT_GELU_TANH);
     else if (a.act == LLMSS_ACT_SILU) LLMSS_SC(EPI_ACT, LLMSS_ACT_SILU);
+    else if (a.act == LLMSS_ACT_RELU2) LLMSS_SC(EPI_ACT, LLMSS_ACT_RELU2);
     else LLMSS_SC(EPI_ACT, ACT_RUNTIME);
   } else if (a.epi == EPI_GATED) {
     if (a.act == LLMSS_ACT_SILU) LLMSS_SC(EPI_GATED, LLMSS_ACT_SILU);
@@ -332,6 +334,7 @@ __device__ __forceinline__ bool store_chunk_full(const GemmArgs& a, const float 
   } else if (a.epi == EPI_ACT) {
     if (a.act == LLMSS_ACT_GELU_TANH) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_GELU_TANH>(a, v, n, mb0, lane, bval);
     else if (a.act == LLMSS_ACT_SILU) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_SILU>(a, v, n, mb0, lane, bval);
+    else if (a.act == LLMSS_ACT_RELU2) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_RELU2>(a, v, n, mb0, lane, bval);
     else store_chunk_full_t<T, CH, EPI_ACT, ACT_RUNTIME>(a, v, n, mb0, lane, bval);
   } else if (a.epi == EPI_GATED) {
     if (a.act == LLMSS_ACT_SILU) store_chunk_full_t<T, CH, EPI_GATED, LLMSS_ACT_SILU>(a, v, n, mb0, lane, bval);

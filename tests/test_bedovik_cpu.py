@@ -51,14 +51,16 @@ def tokens_for(cfg, n, seed):
 
 def close(got, want, tol, rows_over=0.0):
     """Largest difference, and root mean square difference, relative to the spread of the expected values.  `rows_over`: share
-    of rows that may exceed `tol` (up to 4 x): 16-bit runs flip a routing decision now and then where two expert scores
-    nearly tie, which moves that one position; the true 32-bit runs allow none."""
+    of rows that may exceed `tol`: a 16-bit run flips a routing decision now and then where two expert scores nearly tie,
+    which moves that one position by a whole expert's output; those rows are then left out of the root mean square.  The true
+    32-bit runs allow none, and the 16-bit kernels are held to `tol` on every row where no router is involved."""
     got, want = got.double().cpu(), want.double().cpu()
     spread = max(want.std().item(), 1e-6)
     d = (got - want).abs().reshape(got.shape[0], -1).max(-1).values / spread
-    rms = (got - want).pow(2).mean().sqrt().item() / spread
-    over = (d >= tol).sum().item()
-    assert over <= rows_over * d.numel() and d.max().item() < (4 * tol if rows_over else tol) and rms < tol / 4, \
+    ok = d < tol
+    over = (~ok).sum().item()
+    rms = ((got - want)[ok].pow(2).mean().sqrt().item() / spread) if ok.any() else 0.0
+    assert over <= rows_over * d.numel() and rms < tol / 4, \
         f"relative error max {d.max().item():.3g} rms {rms:.3g}, {over} of {d.numel()} rows over {tol}"
 
 
