@@ -26,7 +26,10 @@ from llmss_b200.utils.dist import initialize_torch_distributed
 def get_args(argv=None):
     parser = ArgumentParser()
     parser.add_argument("--pretrained_model_path", type=str, required=True)
-    parser.add_argument("--prompts", type=str, nargs="+", required=True)
+    parser.add_argument("--prompts", type=str, nargs="+", default=None)
+    parser.add_argument("--prompt_ids", type=str, nargs="+", default=None,
+                        help="prompts as token ids ('5 17 3' '8 9'): for checkpoints that ship no tokenizer (native architectures); "
+                             "the continuations are printed as ids too")
     parser.add_argument("--max_new_tokens", type=int, default=20)
     parser.add_argument("--is_greedy", action="store_true")
     parser.add_argument("--temperature", type=float, default=1.0, help="If you don't wanna use this, set to 1.0")
@@ -51,21 +54,26 @@ def main(argv=None):
     if rank == 0:
         start_time = time()
 
-    from transformers import AutoTokenizer
+    assert (args.prompts is None) != (args.prompt_ids is None), "give either --prompts or --prompt_ids"
+    tokenizer = None
+    if args.prompts is not None:
+        from transformers import AutoTokenizer
 
-    tokenizer = AutoTokenizer.from_pretrained(args.pretrained_model_path, padding_side="left", truncation_side="left")
+        tokenizer = AutoTokenizer.from_pretrained(args.pretrained_model_path, padding_side="left", truncation_side="left")
     device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     comm = comm_for(process_group, device)
     comm.barrier()
 
     engine = Engine.from_pretrained(args.pretrained_model_path, dtype=getattr(torch, args.dtype), device=device,
-                                    process_group=process_group, max_batch=max(1, len(args.prompts)),
+                                    process_group=process_group, max_batch=max(1, len(args.prompts or args.prompt_ids)),
                                     eos_token_id=None, sliding_window=args.sliding_window)
     max_len = engine.runner.max_seq_len
 
     # rank 0 tokenises; ids are shared with one broadcast (reference N5, generate.py:73-85)
-    list_of_prompts = args.prompts
-    if rank == 0:
+    list_of_prompts = args.prompts or args.prompt_ids
+    if rank == 0 and tokenizer is None:
+        payload = [[int(t) for t in p.replace(",", " ").split()][-(max_len - 1):] for p in args.prompt_ids]
+    elif rank == 0:
         enc = tokenizer(list_of_prompts, return_attention_mask=False, truncation=True, max_length=max_len - 1)["input_ids"]
         payload = [list(map(int, e)) for e in enc]
     else:
@@ -82,7 +90,7 @@ def main(argv=None):
         end_time = time()
         print(f"elapsed time: {end_time - start_time}")
         print(f"prompts: {list_of_prompts}")
-        print(f"continuations: {[tokenizer.decode(o) for o in outputs]}")
+        print(f"continuations: {[tokenizer.decode(o) for o in outputs] if tokenizer is not None else outputs}")
     return outputs
 
 

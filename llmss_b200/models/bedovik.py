@@ -99,7 +99,8 @@ def bedovik_spec(config) -> BedovikSpec:
         if lc["type"] not in _MIXERS:
             raise ValueError(f"bedovik: layer {i} has unknown mixer type {lc['type']!r}; have {sorted(_MIXERS)}")
         m = lc["mixer"]
-        mixers.append(MixerSpec(lc["type"], int(m["heads"]), int(m["dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"])))
+        mixers.append(MixerSpec(lc["type"], int(m["heads"]), int(m["dim"]), int(m["vdim"]), int(m["kv_rank"]),
+                                float(m.get("scale", int(m["dim"]) ** -0.5))))
         f = lc.get("mlp")
         if f is None:
             ffns.append(None)

@@ -350,3 +350,16 @@ def test_config_is_read_not_assumed(tmp_path):
     bad = dict(CONFIGS["no_loop"], layers=[dict(CONFIGS["no_loop"]["layers"][0], type="windowed")])
     with pytest.raises(ValueError):
         bedovik_spec(NativeConfig(bad))
+
+
+def test_command_line_generation_with_token_ids(tmp_path):
+    """generate.py serves a checkpoint that ships no tokenizer: prompts and continuations are token ids."""
+    import generate
+
+    cfg = CONFIGS["no_loop"]
+    path = write_random_checkpoint(tmp_path / "cli", cfg, dtype=torch.bfloat16, device="cpu", seed=4)
+    W = oracle.load_weights(path)
+    prompts = [tokens_for(cfg, 6, 70), tokens_for(cfg, 2, 71)]
+    out = generate.main(["--pretrained_model_path", str(path), "--prompt_ids", *[" ".join(map(str, p)) for p in prompts],
+                         "--max_new_tokens", "6", "--is_greedy", "--use_cache", "--dtype", "float32"])
+    assert out == [oracle.greedy(cfg, W, p, 6) for p in prompts]
