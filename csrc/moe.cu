@@ -166,6 +166,76 @@ __global__ void __launch_bounds__(256) moe_scale_kernel(T* __restrict__ a, int64
   }
 }
 
+
+// ---- grouped form for long prompts: (token, chosen expert) pairs sorted by expert, so that every expert multiplies one
+// contiguous block of rows.  count -> (host: offsets) -> permute (ordered compaction, one CTA per expert: the order inside an
+// expert's block is the pair order, so the result does not depend on scheduling) -> gather rows -> per-expert GEMMs ->
+// combine (sum over a token's experts in its own order, 32-bit).
+__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int P, int* __restrict__ counts) {
+  __shared__ int red[8];
+  const int e = blockIdx.x;
+  int c = 0;
+  for (int p = threadIdx.x; p < P; p += 256) c += (ids[p] == e);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    counts[e] = t;
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_permute_kernel(const int* __restrict__ ids, int P, const int* __restrict__ offsets,
+                                                          int* __restrict__ perm, int* __restrict__ inv) {
+  __shared__ int wsum[8];
+  __shared__ int running;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) running = offsets[e];
+  __syncthreads();
+  for (int p0 = 0; p0 < P; p0 += 256) {
+    const int p = p0 + threadIdx.x;
+    const bool mine = p < P && ids[p] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) wsum[warp] = __popc(m);
+    __syncthreads();
+    int before = running;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
+    if (mine) {
+      const int pos = before + __popc(m & ((1u << lane) - 1u));
+      perm[pos] = p;
+      inv[p] = pos;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int t = 0;
+      for (int w = 0; w < 8; ++w) t += wsum[w];
+      running += t;
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_rows_kernel(const T* __restrict__ h, int64_t ldh, const int* __restrict__ perm,
+                                                              int top, T* __restrict__ xs, int W) {
+  const int64_t i = blockIdx.x;
+  const T* src = h + (int64_t)(perm[i] / top) * ldh;
+  for (int c = threadIdx.x; c < W; c += 256) xs[i * W + c] = src[c];
+}
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv,
+                                                          const float* __restrict__ wts, float* __restrict__ out, int64_t ldo,
+                                                          int W, int top) {
+  const int64_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < W; c += 256) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += wts[t * top + k] * y[(int64_t)inv[t * top + k] * W + c];
+    out[t * ldo + c] = v;
+  }
+}
+
 template <typename T>
 int launch_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up, const void* w_down,
                    int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T_, int W, int F, int top, int act, cudaStream_t stream) {
@@ -205,6 +275,37 @@ LLMSS_API int llmss_moe_experts(const void* h, int64_t ldh, const int* ids, cons
 LLMSS_API int llmss_moe_scale(void* a, int64_t lda, const float* dense, int T_, int E, int F, int dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
   LLMSS_BY_DTYPE(dtype, (moe_scale_kernel<T><<<T_, 256, 0, stream>>>((T*)a, lda, dense, E, F)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_moe_count(const int* ids, int P, int E, int* counts, cudaStream_t stream) {
+  if (E <= 0) return 0;
+  moe_count_kernel<<<E, 256, 0, stream>>>(ids, P, counts);
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// offsets[e] = first row of expert e's block; perm[row] = pair index (token * top + k); inv[pair] = row
+LLMSS_API int llmss_moe_permute(const int* ids, int P, int E, const int* offsets, int* perm, int* inv, cudaStream_t stream) {
+  if (E <= 0 || P <= 0) return 0;
+  moe_permute_kernel<<<E, 256, 0, stream>>>(ids, P, offsets, perm, inv);
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_moe_gather_rows(const void* h, int64_t ldh, const int* perm, int top, void* xs, int P, int W, int dtype,
+                                    cudaStream_t stream) {
+  if (P <= 0) return 0;
+  LLMSS_BY_DTYPE(dtype, (moe_gather_rows_kernel<T><<<P, 256, 0, stream>>>((const T*)h, ldh, perm, top, (T*)xs, W)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_moe_combine(const float* y, const int* inv, const float* wts, float* out, int64_t ldo, int T_, int W, int top,
+                                cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  moe_combine_kernel<<<T_, 256, 0, stream>>>(y, inv, wts, out, ldo, W, top);
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -218,6 +218,14 @@ int llmss_moe_route(const float* z, int64_t ldz, int T, int E, int top, int grou
 int llmss_moe_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up, const void* w_down,
                       int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T, int W, int F, int top, int act, int dtype,
                       llmss_stream_t stream);
+/* grouped form: count pairs per expert; (host turns counts into offsets); ordered permutation perm[row] = pair,
+ * inv[pair] = row; gather the pairs' token rows; (per-expert GEMMs on contiguous rows); weighted sum per token */
+int llmss_moe_count(const int* ids, int P, int E, int* counts, llmss_stream_t stream);
+int llmss_moe_permute(const int* ids, int P, int E, const int* offsets, int* perm, int* inv, llmss_stream_t stream);
+int llmss_moe_gather_rows(const void* h, int64_t ldh, const int* perm, int top, void* xs, int P, int W, int dtype,
+                          llmss_stream_t stream);
+int llmss_moe_combine(const float* y, const int* inv, const float* wts, float* out, int64_t ldo, int T, int W, int top,
+                      llmss_stream_t stream);
 int llmss_moe_scale(void* a, int64_t lda, const float* dense, int T, int E, int F, int dtype, llmss_stream_t stream);
 
 /* ---- K10 embedding gather (G1; layers.py:182-214) ---- */

@@ -60,6 +60,9 @@ class LatentAttention:
             return ops.linear(ctx, self.w_o, out_dtype=torch.float32)
 
 
+_GROUPED_ROWS = int(os.environ.get("LLMSS_MOE_GROUPED_MIN_ROWS", "64"))   # grouped form from this many rows per expert on average
+_FORCE_GROUPED = os.environ.get("LLMSS_MOE_FORCE_GROUPED", "0") == "1"
+_GEMM_TFLOPS, _CALL_US = 1200.0, 30.0     # sustained tensor-core rate of the expert GEMMs; host cost of issuing one GEMM
 _DENSE_MIN = int(os.environ.get("LLMSS_MOE_DENSE_MIN_TOKENS", "0"))   # 0: dense as soon as token x top pairs >= experts
 
 
@@ -71,7 +74,11 @@ class RoutedExperts:
     From there on a batch touches about every expert anyway, and 16-bit CUDA batches run the dense form: every expert's
     up-projection in one tensor-core GEMM (activation fused) that streams each weight once, each expert's block
     scaled by its routing weight (0 if not chosen), one GEMM over the side-by-side down matrices.  The dense form
-    spends experts / top times the needed FLOPs; ``LLMSS_MOE_DENSE_MIN_TOKENS`` moves the switch."""
+    spends experts / top times the needed FLOPs, which is nothing while the step is bound by the weight bytes (decode,
+    short portions; it is also free of host synchronisation, so it can sit in a captured decode graph).  Prompts long
+    enough to give every expert ``LLMSS_MOE_GROUPED_MIN_ROWS`` rows on average run the grouped form: pairs sorted by
+    expert on the device, one pair of tensor-core GEMMs per expert over its contiguous rows, 32-bit weighted sum per
+    token.  ``LLMSS_MOE_DENSE_MIN_TOKENS`` moves the gather / dense switch."""
 
     def __init__(self, experts: int, top: int, groups: int, keep: int, route_scale: float, ff: int, act: int = ACT_RELU2):
         if experts % groups or not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
@@ -82,6 +89,16 @@ class RoutedExperts:
     def in_rows(self):
         return self.w_router
 
+    def _grouped_pays(self, T: int, W: int) -> bool:
+        """Dense runs experts / top times the FLOPs in two launches; grouped runs the needed FLOPs in 2 x experts launches that
+        the host issues one by one.  Estimate both (tensor-core rate and per-call host cost measured on B200) and take the
+        cheaper; LLMSS_MOE_GROUPED_MIN_ROWS=1 with LLMSS_MOE_FORCE_GROUPED=1 forces the grouped form."""
+        if _FORCE_GROUPED:
+            return True
+        dense_us = 4.0 * T * self.experts * self.ff * W / (_GEMM_TFLOPS * 1e6)
+        grouped_us = max(2 * self.experts * _CALL_US, dense_us * self.top / self.experts) + 150.0
+        return grouped_us < dense_us
+
     def bind(self, base: int):
         self.z_off = base
         self.w_router = None
@@ -91,6 +108,14 @@ class RoutedExperts:
         E, F = self.experts, self.ff
         z = y[:, self.z_off:self.z_off + E]
         T = h.shape[0]
+        if (h.is_cuda and h.dtype != torch.float32 and T * self.top >= _GROUPED_ROWS * E and self._grouped_pays(T, h.shape[1])
+                and not torch.cuda.is_current_stream_capturing()):
+            from ..ops import cuda_impl as cu
+
+            with trace("experts_route"):
+                ids, wts = ops.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale)
+            with trace("experts_grouped"):
+                return cu.moe_experts_grouped(h, ids, wts, self.w_up, self.w_down, self.act)
         if h.is_cuda and h.dtype != torch.float32 and T >= (_DENSE_MIN or -(-E // self.top)):
             from ..ops import cuda_impl as cu
 

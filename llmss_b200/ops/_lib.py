@@ -115,6 +115,10 @@ _SIGS = {
                                 c_void_p]),
     "llmss_moe_experts": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "llmss_moe_count": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "llmss_moe_permute": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "llmss_moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "llmss_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "llmss_moe_scale": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
 }
 _OPTIONAL = {

@@ -556,3 +556,40 @@ def moe_scale(a, dense, experts: int, ff: int):
     _lib.check(rc, "llmss_moe_scale")
     _count()
     return a
+
+
+def moe_experts_grouped(h, ids, wts, w_up, w_down, act):
+    """Long prompts: sort the (token, expert) pairs by expert on the device and run every expert as one pair of tensor-core
+    GEMMs over its contiguous rows -- top / experts of the dense form's FLOPs.  Reads the per-expert counts on the host (one
+    small synchronising copy), so it is for prompt processing, not for graph-captured decode steps."""
+    lib = _lib.load()
+    T, W, ldh = _rows2d(h)
+    E, F, _ = w_up.shape
+    top = ids.shape[1]
+    P, dev = T * top, h.device
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    _lib.check(lib.llmss_moe_count(_ptr(ids), P, E, _ptr(counts), _stream()), "llmss_moe_count")
+    cnt = counts.tolist()
+    offs, o = [], 0
+    for c in cnt:
+        offs.append(o)
+        o += c
+    offsets = torch.tensor(offs, dtype=torch.int32).to(dev)
+    perm = torch.empty(P, dtype=torch.int32, device=dev)
+    inv = torch.empty(P, dtype=torch.int32, device=dev)
+    _lib.check(lib.llmss_moe_permute(_ptr(ids), P, E, _ptr(offsets), _ptr(perm), _ptr(inv), _stream()), "llmss_moe_permute")
+    xs = torch.empty(P, W, dtype=h.dtype, device=dev)
+    _lib.check(lib.llmss_moe_gather_rows(_ptr(h), ldh, _ptr(perm), top, _ptr(xs), P, W, _DT[h.dtype], _stream()),
+               "llmss_moe_gather_rows")
+    _count(3)
+    a = torch.empty(P, F, dtype=h.dtype, device=dev)
+    y = torch.empty(P, W, dtype=torch.float32, device=dev)
+    for e, (lo, c) in enumerate(zip(offs, cnt)):
+        if c:
+            linear(xs[lo:lo + c], w_up[e], act=act, out=a[lo:lo + c])
+            linear(a[lo:lo + c], w_down[:, e * F:(e + 1) * F], out_dtype=torch.float32, out=y[lo:lo + c])
+    out = torch.empty(T, W, dtype=torch.float32, device=dev)
+    _lib.check(lib.llmss_moe_combine(_ptr(y), _ptr(inv), _ptr(wts), _ptr(out), out.stride(0), T, W, top, _stream()),
+               "llmss_moe_combine")
+    _count()
+    return out

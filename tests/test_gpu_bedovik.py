@@ -83,6 +83,8 @@ def test_tensor_core_paths_through_the_engine(tmp_path, dtype, tol):
     from llmss_b200.models import blocks
 
     old, blocks._DENSE_MIN = blocks._DENSE_MIN, 48
+    old_g, blocks._GROUPED_ROWS = blocks._GROUPED_ROWS, 16      # portions of 64 tokens and more: grouped experts
+    old_f, blocks._FORCE_GROUPED = blocks._FORCE_GROUPED, True
     try:
         cfg, W, eng = cases.build(tmp_path, "tc_ranks", "cuda", dtype)
         assert eng.runner.block_size == 64
@@ -97,7 +99,36 @@ def test_tensor_core_paths_through_the_engine(tmp_path, dtype, tol):
         cases.close(torch.cat([o1[:70], o2[:1]]), want[:71], tol, few)
         cases.close(torch.cat([o1[70:], o2[1:]]), oracle.forward(cfg, W, other)[0], tol, few)
     finally:
-        blocks._DENSE_MIN = old
+        blocks._DENSE_MIN, blocks._GROUPED_ROWS, blocks._FORCE_GROUPED = old, old_g, old_f
+
+
+@pytest.mark.parametrize("dtype,tol", [pytest.param(BF16, 3e-2, id="bf16"), pytest.param(torch.float16, 1e-2, id="f16")])
+def test_expert_forms_agree(dtype, tol):
+    """The three execution forms of the routed experts (per-token gather, dense with zero weights, grouped by expert) against
+    the oracle on the same inputs."""
+    from llmss_b200.models import blocks
+
+    torch.manual_seed(0)
+    T, W, F, E, top = 300, 64, 32, 8, 2
+    ups = [(torch.randn(F, W) * W ** -0.5).to(dtype) for _ in range(E)]
+    downs = [(torch.randn(W, F) * F ** -0.5).to(dtype) for _ in range(E)]
+    ff = blocks.RoutedExperts(E, top, 4, 2, 1.5, F)
+    ff.w_up, ff.w_down, ff.z_off = torch.stack(ups).cuda(), torch.cat(downs, dim=1).contiguous().cuda(), 0
+    h = torch.randn(T, W).to(dtype)
+    z = 2.0 * torch.randn(T, E)
+    want = []
+    for t in range(T):
+        chosen, w = oracle.route(z[t].double(), top, 4, 2, 1.5)
+        want.append(oracle.experts(h[t].double(), chosen, w, [u.double() for u in ups], [d.double() for d in downs]))
+    want = torch.stack(want)
+    keep = blocks._GROUPED_ROWS, blocks._DENSE_MIN, blocks._FORCE_GROUPED
+    blocks._FORCE_GROUPED = True
+    try:
+        for form, (g, d) in {"gather": (10 ** 9, 10 ** 9), "dense": (10 ** 9, 1), "grouped": (1, 1)}.items():
+            blocks._GROUPED_ROWS, blocks._DENSE_MIN = g, d
+            cases.close(ff.forward(h.cuda(), z.cuda()), want, tol)
+    finally:
+        blocks._GROUPED_ROWS, blocks._DENSE_MIN, blocks._FORCE_GROUPED = keep
 
 
 def test_greedy_generation_with_decode_graphs(tmp_path):
