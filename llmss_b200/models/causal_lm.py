@@ -121,7 +121,7 @@ class LlamaForCausalLM(CausalLM):
 
 class BedovikForCausalLM(CausalLM):
     """Native architecture (config.json with an ``architecture`` key, see models/bedovik.py): latent attention, routed
-    experts, Dynamic Tanh, weight-shared loop.  Same constructor / forward contract as the HF-shaped classes."""
+    experts, Dynamic Tanh, weight-shared loop.  Same constructor and forward interface as the HF-shaped classes."""
     family = "bedovik"
 
     def __init__(self, config, weights, fuse_parallel: bool = True):

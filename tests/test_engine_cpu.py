@@ -263,3 +263,23 @@ def test_prefix_cache_covers_generated_tokens_for_follow_up_turns(tmp_path):
     assert a2 == plain.generate([follow], SamplingParams(max_new_tokens=10, is_greedy=True))[0]
     a = eng.runner.alloc
     assert a.num_free == a.num_blocks - 1 and all(x == 0 for x in a.ref)
+
+
+def test_feed_mixed_steps_match_the_hf_logits(tmp_path):
+    """Engine.feed (teacher-forced packed steps: portions of prompts beside single tokens, logits at chosen places) on the
+    multi-head families: every position's logits equal HF's whole-sequence forward, however the tokens were cut."""
+    for family in ("gptj", "llama", "gpt_bigcode"):
+        cfg, hf = make_tiny(family, tmp_path / family)
+        eng = Engine.from_pretrained(str(tmp_path / family), dtype=torch.float32, device="cpu", max_batch=3, max_seq_len=64)
+        g = torch.Generator().manual_seed(5)
+        a, b = (torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (37, 21))
+        with torch.no_grad():
+            want = {k: hf(torch.tensor([t])).logits[0] for k, t in (("a", a), ("b", b))}
+        o1 = eng.feed([("a", a[:20], list(range(20))), ("b", b[:1], [0])], [])
+        o2 = eng.feed([("a", a[20:21], [0]), ("b", b[1:18], list(range(17)))], [])
+        o3 = eng.feed([("a", a[21:], list(range(16))), ("b", b[18:], [0, 2])], ["a", "b"])
+        got_a = torch.cat([o1[:20], o2[:1], o3[:16]])
+        got_b = torch.cat([o1[20:], o2[1:], o3[16:]])
+        assert torch.allclose(got_a, want["a"], atol=2e-4, rtol=1e-4)
+        assert torch.allclose(got_b, want["b"][[*range(18), 18, 20]], atol=2e-4, rtol=1e-4)
+        assert eng.runner.alloc.num_free == eng.runner.alloc.num_blocks - 1
