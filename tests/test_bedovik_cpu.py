@@ -363,3 +363,44 @@ def test_command_line_generation_with_token_ids(tmp_path):
     out = generate.main(["--pretrained_model_path", str(path), "--prompt_ids", *[" ".join(map(str, p)) for p in prompts],
                          "--max_new_tokens", "6", "--is_greedy", "--use_cache", "--dtype", "float32"])
     assert out == [oracle.greedy(cfg, W, p, 6) for p in prompts]
+
+
+def run_trace_runner(tmp_path, device_env, dtype, tol):
+    """bin/trace_run as a user starts it: steps on standard input, `done <n>` lines back, logits files in --out."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    cfg = CONFIGS["mid_loop"]
+    path = write_random_checkpoint(tmp_path / "m", cfg, dtype=torch.bfloat16, device="cpu", seed=2)
+    W = oracle.load_weights(path)
+    a, b = tokens_for(cfg, 70, 80), tokens_for(cfg, 9, 81)
+    want = {"a": oracle.forward(cfg, W, a)[0], "b": oracle.forward(cfg, W, b)[0]}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 5, 32]}, {"id": "b", "tokens": b[:2], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[33:34], "want": [0]}], "end": []},                      # b sits this one out
+        {"step": 2, "entries": [{"id": "b", "tokens": b[2:], "want": [0, 6]}, {"id": "a", "tokens": a[34:66], "want": [31]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[66:], "want": [0, 1, 2, 3]}], "end": ["a"]},
+        {"step": 4, "entries": [{"id": "c", "tokens": b, "want": [8]}], "end": ["c"]},                          # b's pages and slot again
+    ]
+    expect = {0: [("a", 0), ("a", 5), ("a", 32)], 1: [("a", 33)], 2: [("b", 2), ("b", 8), ("a", 65)],
+              3: [("a", 66), ("a", 67), ("a", 68), ("a", 69)], 4: [("b", 8)]}
+    root = Path(__file__).resolve().parents[1]
+    out = tmp_path / "out"
+    env = dict(os.environ, **device_env)
+    p = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(path), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                       text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+    for n, rows in expect.items():
+        got = torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"]))
+        close(got, torch.stack([want[k][i] for k, i in rows]), tol)
+
+
+def test_trace_runner_on_cpu(tmp_path):
+    run_trace_runner(tmp_path, {"LLMSS_TRACE_CPU": "1", "CUDA_VISIBLE_DEVICES": ""}, "float32", TOL)

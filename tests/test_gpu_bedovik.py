@@ -45,7 +45,9 @@ def test_mechanisms(dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", MODES)
-@pytest.mark.parametrize("sizes", [(40, 3, 8, 12, 24), (64, 5, 16, 8, 64), (64, 2, 32, 32, 128), (96, 9, 8, 16, 256), (64, 20, 8, 8, 300)])
+@pytest.mark.parametrize("sizes", [(40, 3, 8, 12, 24), (64, 5, 16, 8, 64), (64, 2, 32, 32, 128), (96, 9, 8, 16, 256), (64, 20, 8, 8, 300),
+                                   (64, 16, 8, 8, 128), (64, 32, 8, 8, 64), (64, 32, 8, 8, 128), (64, 7, 8, 8, 128), (64, 12, 8, 8, 256),
+                                   (64, 8, 8, 8, 256), (64, 64, 8, 8, 64)])
 def test_latent_attention_kernels(dtype, tol, sizes):
     for chunks in ([77], [1] * 40, [5, 2, 17, 1, 1, 9, 2, 40], [64, 64, 3]):
         for gated in (True, False):
@@ -152,3 +154,8 @@ def test_bfloat16_generation_runs_on_graphs(tmp_path):
     lg = eng.feed([("chk", seq, list(range(len(prompts[1]) - 1, len(seq) - 1)))], ["chk"])
     agree = (lg.argmax(-1).cpu() == torch.tensor(out[1])).float().mean().item()
     assert agree >= 0.8
+
+
+@pytest.mark.parametrize("dtype,tol", [pytest.param("float32", 3e-4, id="f32"), pytest.param("bfloat16", 8e-2, id="bf16")])
+def test_trace_runner_on_cuda(tmp_path, dtype, tol):
+    cases.run_trace_runner(tmp_path, {}, dtype, tol)
