@@ -63,6 +63,7 @@ class CausalLMOutputWithPast:
 
 class CausalLM(nn.Module):
     family: str = ""
+    float32_on_cuda: bool = False   # the multi-head families' CUDA kernels take 16-bit activations only
 
     def __init__(self, config, weights, fuse_parallel: bool = True):
         super().__init__()
@@ -123,6 +124,7 @@ class BedovikForCausalLM(CausalLM):
     """Native architecture (config.json with an ``architecture`` key, see models/bedovik.py): latent attention, routed
     experts, Dynamic Tanh, weight-shared loop.  Same constructor and forward interface as the HF-shaped classes."""
     family = "bedovik"
+    float32_on_cuda = True          # every kernel of this family also exists in true 32-bit
 
     def __init__(self, config, weights, fuse_parallel: bool = True):
         nn.Module.__init__(self)
