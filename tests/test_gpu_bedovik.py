@@ -49,8 +49,9 @@ def test_mechanisms(dtype, tol):
                                    (64, 16, 8, 8, 128), (64, 32, 8, 8, 64), (64, 32, 8, 8, 128), (64, 7, 8, 8, 128), (64, 12, 8, 8, 256),
                                    (64, 8, 8, 8, 256), (64, 64, 8, 8, 64)])
 def test_latent_attention_kernels(dtype, tol, sizes):
-    for chunks in ([77], [1] * 40, [5, 2, 17, 1, 1, 9, 2, 40], [64, 64, 3]):
-        for gated in (True, False):
+    many_heads = sizes[1] >= 12      # the oracle loops over heads in Python: fewer cuttings there
+    for chunks in (([5, 2, 17, 1, 1, 9, 2, 40],) if many_heads else ([77], [1] * 40, [5, 2, 17, 1, 1, 9, 2, 40], [64, 64, 3])):
+        for gated in ((True,) if many_heads else (True, False)):
             cases.test_latent_attention_ops(gated, chunks, "cuda", dtype, tol, sizes)
 
 
