@@ -392,8 +392,9 @@ def run_trace_runner(tmp_path, device_env, dtype, tol):
     root = Path(__file__).resolve().parents[1]
     out = tmp_path / "out"
     env = dict(os.environ, **device_env)
+    # --max-tokens 192: 70 and 9 tokens are live at once, each rounded up to whole 64-token pages
     p = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(path), "--dtype", dtype, "--out", str(out),
-                        "--max-tokens", "192"],     # live at once: 70 and 9 tokens, each rounded up to 64-token pages input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                        "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
                        text=True, env=env, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
