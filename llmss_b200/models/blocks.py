@@ -8,7 +8,6 @@ arguments.
 from __future__ import annotations
 
 import os
-from typing import Optional
 
 import torch
 

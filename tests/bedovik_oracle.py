@@ -7,7 +7,6 @@ every call recomputes whole sequences with explicit loops over tokens, heads and
 Notation: W = width, H = heads, d = query / key size per head, dv = value size per head, R = latent rank,
 E = experts, F = expert hidden size.  Linear weights are [out, in].
 """
-import math
 
 import torch
 

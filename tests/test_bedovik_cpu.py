@@ -2,7 +2,6 @@
 
 Own small configurations and random weights; the same cases run on CUDA in test_gpu_bedovik.py.
 """
-import math
 
 import pytest
 import torch
@@ -405,3 +404,14 @@ def run_trace_runner(tmp_path, device_env, dtype, tol):
 
 def test_trace_runner_on_cpu(tmp_path):
     run_trace_runner(tmp_path, {"LLMSS_TRACE_CPU": "1", "CUDA_VISIBLE_DEVICES": ""}, "float32", TOL)
+
+
+def test_model_call_with_past_state(tmp_path):
+    """The registry class called like the other families' classes: model(input_ids, past_key_values) -> logits [B, S, V]."""
+    cfg, W, eng = build(tmp_path, "no_loop")
+    toks = tokens_for(cfg, 30, 90)
+    want, _ = oracle.forward(cfg, W, toks)
+    ids = torch.tensor([toks])
+    out = eng.model(ids[:, :21], use_cache=True)
+    out2 = eng.model(ids[:, 21:], past_key_values=out.past_key_values, use_cache=True)
+    close(torch.cat([out.logits[0], out2.logits[0]]), want, TOL)
