@@ -176,12 +176,11 @@ def test_latent_attention_ops(gated, chunks, device="cpu", dtype=torch.float32, 
 
 @pytest.mark.parametrize("far", [0, 3, 15, 16, 31, 32, 63, 64, 200, 255, 256, 399])
 @pytest.mark.parametrize("q_len", [1, 2, 9])
-def test_one_key_stands_out(far, q_len, device="cpu", dtype=torch.float32, R=24, block_size=16, tol=1e-3):
+def test_one_key_stands_out(far, q_len, device="cpu", dtype=torch.float32, R=24, block_size=16, tol=1e-3, ctx=400):
     """Random latents in the cache; the query of the last token is a large multiple of ONE cached latent, so that key takes
     (almost) all of the softmax: the output must be that latent.  The key sits far back, on page borders, first in the
     sequence; the query is decoded alone or is the end of a portion.  A kernel that skips or misreads the key returns a blend
     of other latents instead."""
-    ctx = 400
     far = min(far, ctx - 1)
     g = torch.Generator().manual_seed(far)
     lat = torch.randn(ctx, R, generator=g)

@@ -61,6 +61,10 @@ def test_far_keys_and_page_borders(dtype, tol, R, bs):
     for far in (0, 3, 15, 16, 63, 64, 65, 127, 128, 255, 256, 320, 398, 399):
         for q_len in (1, 2, 9):
             cases.test_one_key_stands_out(far, q_len, "cuda", dtype, R, bs, tol)
+    # a context long enough for the decode kernels to split the key range and merge the partial softmaxes
+    for far in (0, 255, 256, 257, 511, 512, 700, 1023, 1024, 1099):
+        for q_len in (1, 5):
+            cases.test_one_key_stands_out(far, q_len, "cuda", dtype, R, bs, tol, ctx=1100)
     cases.test_window_edges_of_causality("cuda", dtype, 2e-3 if dtype == F32 else 3e-2)
 
 
