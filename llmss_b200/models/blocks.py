@@ -41,6 +41,10 @@ class LatentAttention:
         self.c_off = base + self.heads * self.dim
         self.g_off = self.c_off + self.rank if self.gated else -1
         self.w_q = self.w_dkv = self.w_g = None      # live on inside the layer's fused operand
+        # W_uk is stored [(head, dim), rank]; the absorb product contracts over dim, so keep it as [(head, rank), dim]:
+        # contraction index contiguous, the layout the per-head kernel stages with whole 16-byte vectors
+        H, d, R = self.heads, self.dim, self.rank
+        self.w_uk = self.w_uk.view(H, d, R).transpose(1, 2).contiguous().view(H * R, d)
         return self.c_off + self.rank + (self.heads if self.gated else 0)
 
     def forward(self, y, batch, cache, dtype):
@@ -50,7 +54,7 @@ class LatentAttention:
             q, gate = ops.latent_prep(y, self.q_off, self.c_off, self.g_off, H * self.dim, R, H, self.norm_w, self.eps,
                                       batch.slot_mapping, cache, dtype)
         with trace("latent_absorb"):
-            q_abs = ops.heads_matmul(q, self.w_uk, H, self.dim, R, True, out_dtype=ops.latent_query_dtype(cache, H, R))
+            q_abs = ops.heads_matmul(q, self.w_uk, H, self.dim, R, False, out_dtype=ops.latent_query_dtype(cache, H, R))
         with trace("latent_attention"):
             o_lat = ops.latent_attention(q_abs, cache, batch, H, R, self.scale, dtype)
         with trace("latent_unabsorb"):
