@@ -123,6 +123,12 @@ __device__ __forceinline__ float act_apply(float x, int act) {
   }
 }
 
+// the same with full-precision exponentials: true 32-bit paths and everything that feeds a recurrence
+__device__ __forceinline__ float act_exact(float x, int act) {
+  if (act == LLMSS_ACT_SILU) return x / (1.0f + expf(-x));
+  return act_apply(x, act);
+}
+
 // ---------------------------------------------------------------- warp / block reductions
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(256) moe_up_kernel(const T* __restrict__ h, int64_t ldh, const int* __restrict__ ids,
                                                      const T* __restrict__ w_up, T* __restrict__ act_out, int W, int F,
-                                                     int top, int act) {
+                                                     int top, int act, int gated) {
   extern __shared__ float hs[];
   const int64_t t = blockIdx.x;
   const int k = blockIdx.y;
@@ -125,6 +125,15 @@ __global__ void __launch_bounds__(256) moe_up_kernel(const T* __restrict__ h, in
   if (f >= F) return;
   const int lane = threadIdx.x & 31;
   const int e = ids[t * top + k];
+  if (gated) {   // rows interleave (gate_f, up_f): hidden = act(gate) * up
+    const T* wg = w_up + ((int64_t)e * 2 * F + 2 * f) * W;
+    const T* wu = wg + W;
+    float g = 0.f, u = 0.f;
+    for (int c = lane; c < W; c += 32) { g = fmaf(to_f32(wg[c]), hs[c], g); u = fmaf(to_f32(wu[c]), hs[c], u); }
+    g = warp_sum(g); u = warp_sum(u);
+    if (lane == 0) act_out[(t * top + k) * F + f] = from_f32<T>(act_exact(g, act) * u);
+    return;
+  }
   const T* wr = w_up + ((int64_t)e * F + f) * W;
   float s = 0.f;
   for (int c = lane; c < W; c += 32) s = fmaf(to_f32(wr[c]), hs[c], s);
@@ -238,12 +247,13 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 
 template <typename T>
 int launch_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up, const void* w_down,
-                   int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T_, int W, int F, int top, int act, cudaStream_t stream) {
+                   int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T_, int W, int F, int top, int act, int gated,
+                   cudaStream_t stream) {
   const size_t sm_up = (size_t)W * 4, sm_dn = (size_t)top * F * 4;
   static PerDeviceSmem g1, g2;
   LLMSS_CHECK_CUDA(g1.ensure(moe_up_kernel<T>, (int)sm_up));
   LLMSS_CHECK_CUDA(g2.ensure(moe_down_kernel<T>, (int)sm_dn));
-  moe_up_kernel<T><<<dim3(T_, top, (F + 7) / 8), 256, sm_up, stream>>>((const T*)h, ldh, ids, (const T*)w_up, (T*)act_scratch, W, F, top, act);
+  moe_up_kernel<T><<<dim3(T_, top, (F + 7) / 8), 256, sm_up, stream>>>((const T*)h, ldh, ids, (const T*)w_up, (T*)act_scratch, W, F, top, act, gated);
   moe_down_kernel<T><<<dim3(T_, (W + 7) / 8), 256, sm_dn, stream>>>((const T*)act_scratch, ids, wts, (const T*)w_down, ldd, out, ldo, W, F, top);
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -265,11 +275,11 @@ LLMSS_API int llmss_moe_route(const float* z, int64_t ldz, int T_, int E, int to
 
 LLMSS_API int llmss_moe_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up,
                                 const void* w_down, int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T_, int W, int F, int top,
-                                int act, int dtype, cudaStream_t stream) {
+                                int act, int gated, int dtype, cudaStream_t stream) {
   LLMSS_REQUIRE(T_ <= 0x7fffffff / 1 && top <= 65535 && (F + 7) / 8 <= 65535 && (W + 7) / 8 <= 65535, "moe_experts: grid too large");
   LLMSS_REQUIRE((size_t)W * 4 <= 200 * 1024 && (size_t)top * F * 4 <= 200 * 1024, "moe_experts: width %d / top * ff %d exceed shared memory", W, top * F);
   if (T_ == 0) return 0;
-  LLMSS_BY_DTYPE(dtype, return (launch_experts<T>(h, ldh, ids, wts, w_up, w_down, ldd, act_scratch, out, ldo, T_, W, F, top, act, stream)));
+  LLMSS_BY_DTYPE(dtype, return (launch_experts<T>(h, ldh, ids, wts, w_up, w_down, ldd, act_scratch, out, ldo, T_, W, F, top, act, gated, stream)));
 }
 
 LLMSS_API int llmss_moe_scale(void* a, int64_t lda, const float* dense, int T_, int E, int F, int dtype, cudaStream_t stream) {

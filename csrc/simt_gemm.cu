@@ -28,7 +28,7 @@ struct BgArgs {
 
 __device__ __forceinline__ float act_sq(float x, int act) {
   if (act == LLMSS_ACT_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
-  return act_apply(x, act);
+  return act_exact(x, act);
 }
 
 template <typename T, bool OUT_F32>

@@ -216,8 +216,8 @@ int llmss_moe_route(const float* z, int64_t ldz, int T, int E, int top, int grou
 /* out[t] = sum_k wts[t,k] * W_down[ids[t,k]] act(W_up[ids[t,k]] h[t]); w_up [E, F, W]; w_down [W, E * F] (the experts' down matrices side by side,
  * row stride ldd); act_scratch [T, top, F] */
 int llmss_moe_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up, const void* w_down,
-                      int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T, int W, int F, int top, int act, int dtype,
-                      llmss_stream_t stream);
+                      int64_t ldd, void* act_scratch, float* out, int64_t ldo, int T, int W, int F, int top, int act, int gated,
+                      int dtype, llmss_stream_t stream);   /* gated: w_up rows interleave (gate_f, up_f), hidden = act(gate) * up */
 /* grouped form: count pairs per expert; (host turns counts into offsets); ordered permutation perm[row] = pair,
  * inv[pair] = row; gather the pairs' token rows; (per-expert GEMMs on contiguous rows); weighted sum per token */
 int llmss_moe_count(const int* ids, int P, int E, int* counts, llmss_stream_t stream);

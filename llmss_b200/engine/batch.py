@@ -22,10 +22,12 @@ class BatchInput:
     is_decode: bool             # exactly one query token per sequence
     is_fresh_prefill: bool      # no sequence has prior context (seq_len == q_len)
     decode_splits: int = 0      # split-KV factor frozen at graph-capture time (0 = choose per call)
+    state_slots: Optional[torch.Tensor] = None   # [B] int32 state slot of each sequence (recurrent models); < 0 = inert row
 
     @staticmethod
     def build(token_lists: Sequence[Sequence[int]], context_lens: Sequence[int], block_tables: Sequence[Sequence[int]],
-              block_size: int, device, max_blocks: Optional[int] = None, pad_to: int = 1) -> "BatchInput":
+              block_size: int, device, max_blocks: Optional[int] = None, pad_to: int = 1,
+              state_slots: Optional[Sequence[int]] = None) -> "BatchInput":
         """Host-side construction: ``token_lists[i]`` are the new tokens of sequence i, which
         already has ``context_lens[i]`` tokens in the cache blocks ``block_tables[i]``."""
         toks: List[int] = []
@@ -61,4 +63,5 @@ class BatchInput:
             seq_lens=torch.tensor(seq_lens, **i32).to(device), cu_q=torch.tensor(cu, **i32).to(device),
             last_idx=(torch.tensor(cu[1:], dtype=torch.int64) - 1).to(device),
             num_seqs=B, max_q=max(qlens) if qlens else 0, max_kv=max(seq_lens) if seq_lens else 0,
-            is_decode=all(q == 1 for q in qlens), is_fresh_prefill=all(c == 0 for c in context_lens))
+            is_decode=all(q == 1 for q in qlens), is_fresh_prefill=all(c == 0 for c in context_lens),
+            state_slots=None if state_slots is None else torch.tensor(list(state_slots), **i32).to(device))

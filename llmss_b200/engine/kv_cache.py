@@ -113,3 +113,72 @@ class BlockAllocator:
                     self.evictable[b] = None      # most recently used end
                 else:
                     self.free.append(b)
+
+
+class HybridCache:
+    """Cache of models that mix attention layers with recurrent ones.
+
+    Two kinds of storage behind one object: *pages* for the keys and values of attention layers -- planes
+    ``[num_blocks, kv_heads, block_size, dk]`` and ``[num_blocks, kv_heads, block_size, dv]`` (key and value sizes may
+    differ), addressed through the same block tables, slot mapping and ``BlockAllocator`` as ``KVCache`` -- and *state
+    slots* for everything a sequence carries from token to token in constant size: recurrent states, the tails of short
+    convolutions, the previous token or activation.  Every state tensor is ``[num_slots, *shape]``; a sequence owns row
+    ``slot`` of all of them from its first token to its release (``SlotAllocator``).  States are not cleared when a slot
+    changes hands: the kernels start from zeros whenever a sequence's first row is its position 0.
+
+    ``kv_layers``: {layer key: (kv_heads, dk, dv)}; ``states``: {(layer key, name): (shape, dtype)}."""
+
+    def __init__(self, kv_layers, states, num_blocks: int, block_size: int, num_slots: int, dtype, device):
+        self.num_blocks, self.block_size, self.num_slots = num_blocks, block_size, num_slots
+        self.kv_layers = dict(kv_layers)
+        self.num_layers = len(self.kv_layers)
+        self.kplanes = {key: torch.zeros(num_blocks, h, block_size, dk, dtype=dtype, device=device)
+                        for key, (h, dk, dv) in self.kv_layers.items()}
+        self.vplanes = {key: torch.zeros(num_blocks, h, block_size, dv, dtype=dtype, device=device)
+                        for key, (h, dk, dv) in self.kv_layers.items()}
+        self.states = {key: torch.zeros(num_slots, *shape, dtype=dt, device=device) for key, (shape, dt) in states.items()}
+
+    def k(self, layer) -> torch.Tensor:
+        return self.kplanes[layer]
+
+    def v(self, layer) -> torch.Tensor:
+        return self.vplanes[layer]
+
+    def state(self, layer, name: str) -> torch.Tensor:
+        return self.states[(layer, name)]
+
+    @staticmethod
+    def bytes_per_block(kv_layers, block_size, dtype) -> int:
+        return sum(h * (dk + dv) for h, dk, dv in kv_layers.values()) * block_size * torch.empty((), dtype=dtype).element_size()
+
+    def state_bytes_per_slot(self) -> int:
+        return sum(t[0].numel() * t.element_size() for t in self.states.values())
+
+    def copy_blocks_from(self, old: "HybridCache", src: int, dst: int, n: int):
+        """Pages src..src+n of ``old`` become pages dst.. here; the state slots (same numbering) come along."""
+        for key in self.kplanes:
+            self.kplanes[key][dst:dst + n] = old.kplanes[key][src:src + n]
+            self.vplanes[key][dst:dst + n] = old.vplanes[key][src:src + n]
+        for key, t in self.states.items():
+            t.copy_(old.states[key])
+
+
+class SlotAllocator:
+    """Free list over the state slots of a HybridCache: one slot per live sequence."""
+
+    def __init__(self, num_slots: int):
+        self.num_slots = num_slots
+        self.free: List[int] = list(range(num_slots - 1, -1, -1))
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise MemoryError(f"no free state slot: all {self.num_slots} are held by live sequences")
+        return self.free.pop()
+
+    def release(self, slot: int):
+        assert 0 <= slot < self.num_slots and slot not in self.free, f"state slot {slot} released twice"
+        self.free.append(slot)

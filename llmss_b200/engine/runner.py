@@ -23,7 +23,7 @@ from .. import ops
 from ..models.decoder import DecoderLM
 from ..utils.metrics import METRICS
 from .batch import BatchInput
-from .kv_cache import BlockAllocator
+from .kv_cache import BlockAllocator, SlotAllocator
 
 _BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -62,7 +62,7 @@ def request_seed(params: "SamplingParams", seq_id: int) -> int:
 
 class SeqState:
     __slots__ = ("seq_id", "prompt", "output", "blocks", "params", "length", "slot", "finished", "eos", "reserved",
-                 "dropped")
+                 "dropped", "state_slot")
 
     def __init__(self, seq_id, prompt, params, eos=None):
         self.seq_id, self.prompt, self.params = seq_id, list(prompt), params
@@ -74,6 +74,7 @@ class SeqState:
         self.eos = eos
         self.reserved = 0        # cache blocks promised to this sequence at admission (worst case)
         self.dropped = 0         # sliding window: tokens (whole blocks) already evicted from the front of the cache
+        self.state_slot = -1     # recurrent models: row of the cache's state tensors that belongs to this sequence
 
 
 class ModelRunner:
@@ -85,29 +86,39 @@ class ModelRunner:
         self.device, self.dtype = core.device, core.dtype
         self.max_batch = max_batch
         self.prefill_chunk = prefill_chunk   # tokens per sequence and prefill round (None: whole prompts at once)
+        if block_size is None:
+            block_size = core.default_block_size()   # the page size the model's attention kernels like best
+        if max_seq_len is None and hasattr(self.spec, "default_seq_len"):
+            # a model without a positional limit: as long as the pool it is given, else its own default
+            max_seq_len = -(-pool_tokens // block_size) * block_size if pool_tokens else self.spec.default_seq_len
         self.max_seq_len = min(max_seq_len or self.spec.max_pos, self.spec.max_pos)
+        # models with recurrent layers carry constant-size state per sequence: one state slot each, no sharing of pages
+        # between sequences (a cached prefix has no state to resume from) and no eviction of old pages
+        self.recurrent = bool(getattr(core, "needs_state", False))
         # Sliding window (the working form of what the reference attempts at generate.py:133-144, quirk Q7): a sequence
         # that reaches max_seq_len keeps generating over its most recent tokens; the cache evicts whole blocks from the
         # front (block table shifted left, block returned to the pool) and positions stay absolute, which rotary
         # embeddings allow (keys keep the rotation of the position they were written at).  Families with a learned
         # position table cannot index past it, so they keep stopping at max_seq_len.
-        self.sliding = bool(sliding_window) and not self.spec.learned_pos
-        if block_size is None:
-            block_size = core.default_block_size()   # the page size the model's attention kernels like best
+        self.sliding = bool(sliding_window) and not self.spec.learned_pos and not self.recurrent
         self.block_size = block_size
         self.max_blocks_per_seq = -(-self.max_seq_len // block_size)
         if num_blocks is None and pool_tokens:
             num_blocks = 1 + -(-pool_tokens // block_size)    # a pool for this many live tokens, in whole pages
         if num_blocks is None:
             num_blocks = 1 + max_batch * self.max_blocks_per_seq
-        self.kv = core.make_cache(num_blocks, block_size)   # multi-head K / V pages, or latent planes: the model knows
+        # multi-head K / V pages, latent planes, or pages plus state slots: the model knows
+        self.kv = core.make_cache(num_blocks, block_size, max_seqs=max_batch)
         self.alloc = BlockAllocator(num_blocks)
+        self.slots = SlotAllocator(max_batch) if self.recurrent else None
         self._outstanding = 0   # blocks reserved at admission and not yet allocated
         # Prefix cache: full prompt blocks stay registered after their sequence has gone; a later prompt that starts with
         # the same tokens re-uses the blocks (reference-counted) and only computes what follows -- the queries then run
         # over prior context, the paged mode of the prefill attention kernel.  The index is a trie over blocks:
         # (parent node, the block's tokens) -> (node id, block); node ids are never re-used, so entries below an
         # evicted block can no longer be reached.
+        if prefix_cache and self.recurrent:
+            raise ValueError("prefix_cache: a model with recurrent layers cannot resume from cached pages alone")
         self.prefix_enabled = bool(prefix_cache)
         self._nodes: Dict[tuple, tuple] = {}
         self._block_key: Dict[int, tuple] = {}
@@ -131,7 +142,7 @@ class ModelRunner:
         mb = self.max_blocks_per_seq
         # ONE int32 staging buffer per direction: [tokens | positions | slots | seq_lens | block_tables].
         # The token region doubles as the sampler output, so a step is one H2D and one D2H copy.
-        self.n_meta = 4 * B + B * mb
+        self.n_meta = 4 * B + B * mb + B      # ... | state slots (recurrent models)
         pin = self.cuda
         self.h_in = torch.zeros(self.n_meta, dtype=torch.int32, pin_memory=pin)
         self.d_in = torch.zeros(self.n_meta, dtype=torch.int32, device=self.device)
@@ -147,12 +158,15 @@ class ModelRunner:
         self.np_out = self.h_out.numpy()
         self.np_tok, self.np_pos = self.np_in[0:B], self.np_in[B:2 * B]
         self.np_slot, self.np_slen = self.np_in[2 * B:3 * B], self.np_in[3 * B:4 * B]
-        self.np_bt = self.np_in[4 * B:].reshape(B, mb)
+        self.np_bt = self.np_in[4 * B:4 * B + B * mb].reshape(B, mb)
+        self.np_sslot = self.np_in[4 * B + B * mb:]
+        self.np_sslot_row = np.full(B, -1, dtype=np.int64)   # state slot of the sequence bound to each row
         self.np_len = np.zeros(B, dtype=np.int64)       # tokens already in the cache, per row
         self.np_nblk = np.zeros(B, dtype=np.int64)      # blocks owned, per row
         self.np_active = np.zeros(B, dtype=bool)
         self.np_drop = np.zeros(B, dtype=np.int64)      # sliding window: tokens evicted from the front, per row
         self.np_slot[:] = -1
+        self.np_sslot[:] = -1
         self.d_in.copy_(self.h_in)
         # sampler parameters (change only when the batch composition changes)
         self.h_samp_i = torch.zeros(2 * B, dtype=torch.int32, pin_memory=pin)     # [greedy | top_k]
@@ -168,7 +182,7 @@ class ModelRunner:
     def _dev_views(self, B: int):
         buf, MB, mb = self.d_in, self.max_batch, self.max_blocks_per_seq
         return (buf[0:B], buf[MB:MB + B], buf[2 * MB:2 * MB + B], buf[3 * MB:3 * MB + B],
-                buf[4 * MB:].view(MB, mb)[:B])
+                buf[4 * MB:4 * MB + MB * mb].view(MB, mb)[:B], buf[4 * MB + MB * mb:4 * MB + MB * mb + B])
 
     # ------------------------------------------------------------------ sequences
     def blocks_needed(self, n_tokens: int) -> int:
@@ -191,6 +205,8 @@ class ModelRunner:
         self._outstanding += seq.reserved
 
     def _grow(self, seq: SeqState, total_len: int):
+        if self.recurrent and seq.state_slot < 0:
+            seq.state_slot = self.slots.alloc()
         need = self.blocks_needed(total_len) - len(seq.blocks)
         if need > 0:
             seq.blocks.extend(self.alloc.alloc(need))
@@ -247,17 +263,21 @@ class ModelRunner:
             self._register_blocks(seq, (seq.prompt + seq.output)[:seq.length])
         self.alloc.release(seq.blocks)
         seq.blocks = []
+        if seq.state_slot >= 0:
+            self.slots.release(seq.state_slot)
+            seq.state_slot = -1
         self._outstanding -= seq.reserved
         seq.reserved = 0
 
     # ------------------------------------------------------------------ packed steps
-    def _run_packed(self, token_lists, context_lens, block_tables, rows=None) -> torch.Tensor:
+    def _run_packed(self, token_lists, context_lens, block_tables, rows=None, state_slots=None) -> torch.Tensor:
         """THE step function for anything that is not a graph-replayed decode step: sequence i is fed
         ``token_lists[i]`` on top of ``context_lens[i]`` cached tokens (any mix of whole prompts, portions of prompts
         and single tokens; the attention op picks its kernel from the batch shape).  Returns fp32 logits, one row
         per sequence (its last token), or for the packed row indices ``rows``."""
         batch = BatchInput.build(token_lists, context_lens, block_tables, self.block_size, self.device,
-                                 max_blocks=self.max_blocks_per_seq, pad_to=self.core.tp * 16 if self.core.tp > 1 else 1)
+                                 max_blocks=self.max_blocks_per_seq, pad_to=self.core.tp * 16 if self.core.tp > 1 else 1,
+                                 state_slots=state_slots if self.recurrent else None)
         self.stats["prefill_tokens"] += int(batch.tokens.numel())
         if rows is None:
             return self.core.forward(batch, self.kv, last_only=True)
@@ -280,7 +300,8 @@ class ModelRunner:
         for i, toks in enumerate(token_lists):
             rows += [base + j for j in (want[i] if want is not None else [len(toks) - 1])]
             base += len(toks)
-        logits = self._run_packed(token_lists, [s.length for s in seqs], [s.blocks for s in seqs], rows)
+        logits = self._run_packed(token_lists, [s.length for s in seqs], [s.blocks for s in seqs], rows,
+                                  state_slots=[s.state_slot for s in seqs])
         for s, toks in zip(seqs, token_lists):
             s.length += len(toks)
         return logits[:, :self.spec.vocab]
@@ -305,7 +326,8 @@ class ModelRunner:
         for r in range(rounds):
             live = [(i, s) for i, s in enumerate(seqs) if todo[i] > r * chunk]
             logits = self._run_packed([s.prompt[have[i] + r * chunk:have[i] + (r + 1) * chunk] for i, s in live],
-                                      [have[i] + r * chunk for i, _ in live], [s.blocks for _, s in live])
+                                      [have[i] + r * chunk for i, _ in live], [s.blocks for _, s in live],
+                                      state_slots=[s.state_slot for _, s in live])
             for row, (i, s) in enumerate(live):
                 if todo[i] <= (r + 1) * chunk:
                     final_logits[i] = logits[row]
@@ -342,6 +364,8 @@ class ModelRunner:
         rng = torch.zeros(MB, 2, dtype=torch.int32)
         self.np_in[:] = 0
         self.np_slot[:] = -1
+        self.np_sslot[:] = -1
+        self.np_sslot_row[:] = -1
         self.np_active[:] = False
         self.np_len[:] = 0
         self.np_nblk[:] = 0
@@ -365,6 +389,7 @@ class ModelRunner:
             self.np_drop[i] = s.dropped
             self.np_nblk[i] = len(s.blocks)
             self.np_bt[i, :len(s.blocks)] = s.blocks
+            self.np_sslot_row[i] = s.state_slot
             if s.output:
                 self.np_tok[i] = s.output[-1]
         self.d_samp_i.copy_(self.h_samp_i, non_blocking=True)
@@ -408,6 +433,7 @@ class ModelRunner:
         self.np_pos[:] = np.where(act, pos, 0)
         self.np_slot[:] = np.where(act, blk * bs + w % bs, -1)
         self.np_slen[:] = np.where(act, w + 1, 0)
+        self.np_sslot[:] = np.where(act, self.np_sslot_row, -1)
 
     def _vp_greedy(self) -> int:
         """Vocab-parallel token choice (no [B, V] logits all-gather) at TP > 1 on CUDA: 1 = every bound request is
@@ -424,11 +450,12 @@ class ModelRunner:
         return 3 if self._vp_plain_rows else 2
 
     def _decode_body(self, Bp: int, splits: int, vp_greedy: int = 0):
-        tok, pos, slot, slen, bt = self._dev_views(Bp)
+        tok, pos, slot, slen, bt, sslot = self._dev_views(Bp)
         MB = self.max_batch
         batch = BatchInput(tokens=tok, positions=pos, slot_mapping=slot, block_tables=bt, seq_lens=slen,
                            cu_q=self.d_cu[:Bp + 1], last_idx=self.d_last_idx[:Bp], num_seqs=Bp, max_q=1,
-                           max_kv=self.max_seq_len, is_decode=True, is_fresh_prefill=False, decode_splits=splits)
+                           max_kv=self.max_seq_len, is_decode=True, is_fresh_prefill=False, decode_splits=splits,
+                           state_slots=sslot if self.recurrent else None)
         # the sampler writes into the token region: it is both this step's result and the next
         # step's input (device-side feedback loop; no host round trip needed between steps)
         if vp_greedy:
@@ -509,6 +536,7 @@ class ModelRunner:
         inert = torch.zeros_like(self.h_in)
         MB = self.max_batch
         inert[2 * MB:3 * MB] = -1
+        inert[4 * MB + MB * self.max_blocks_per_seq:] = -1
         self.d_in.copy_(inert)
         torch.cuda.synchronize()
         self.core.comm.barrier()

@@ -145,7 +145,7 @@ class BedovikLM(nn.Module):
     def default_block_size(self) -> int:
         return 64 if self.device.type == "cuda" else 16
 
-    def make_cache(self, num_blocks: int, block_size: int) -> LatentCache:
+    def make_cache(self, num_blocks: int, block_size: int, max_seqs=None) -> LatentCache:
         return LatentCache([self.spec.mixers[i].rank for i, _ in self.runs], num_blocks, block_size, self.dtype, self.device)
 
     def num_parameters_local(self) -> int:

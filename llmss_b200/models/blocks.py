@@ -83,11 +83,15 @@ class RoutedExperts:
     expert on the device, one pair of tensor-core GEMMs per expert over its contiguous rows, 32-bit weighted sum per
     token.  ``LLMSS_MOE_DENSE_MIN_TOKENS`` moves the gather / dense switch."""
 
-    def __init__(self, experts: int, top: int, groups: int, keep: int, route_scale: float, ff: int, act: int = ACT_RELU2):
+    def __init__(self, experts: int, top: int, groups: int, keep: int, route_scale: float, ff: int, act: int = ACT_RELU2,
+                 gated: bool = False):
         if experts % groups or not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
             raise ValueError(f"routed experts: bad routing sizes experts={experts} groups={groups} keep={keep} top={top}")
         self.experts, self.top, self.groups, self.keep, self.route_scale, self.ff, self.act = experts, top, groups, keep, route_scale, ff, act
-        self.w_router = self.w_up = self.w_down = None     # [E, W] | [E, F, W] | [W, E * F]
+        # gated: the hidden activation is act(W_gate h) * (W_up h); w_up then holds [E, 2 F, W], rows interleaved (gate_f, up_f)
+        self.gated = gated
+        self.z_off = 0
+        self.w_router = self.w_up = self.w_down = None     # [E, W] | [E, F or 2 F, W] | [W, E * F]
 
     def in_rows(self):
         return self.w_router
@@ -107,8 +111,13 @@ class RoutedExperts:
         self.w_router = None
         return base + self.experts
 
-    def forward(self, h, y):
+    def forward(self, h, y=None):
+        """``y``: a fused projection that holds the router logits at ``z_off`` (32-bit); without it the router runs as
+        a GEMM of its own (32-bit accumulation and output)."""
         E, F = self.experts, self.ff
+        if y is None:
+            with trace("experts_router"):
+                y = ops.linear(h, self.w_router, out_dtype=torch.float32)
         z = y[:, self.z_off:self.z_off + E]
         T = h.shape[0]
         if (h.is_cuda and h.dtype != torch.float32 and T * self.top >= _GROUPED_ROWS * E and self._grouped_pays(T, h.shape[1])
@@ -118,18 +127,18 @@ class RoutedExperts:
             with trace("experts_route"):
                 ids, wts = ops.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale)
             with trace("experts_grouped"):
-                return cu.moe_experts_grouped(h, ids, wts, self.w_up, self.w_down, self.act)
+                return cu.moe_experts_grouped(h, ids, wts, self.w_up, self.w_down, self.act, self.gated)
         if h.is_cuda and h.dtype != torch.float32 and T >= (_DENSE_MIN or -(-E // self.top)):
             from ..ops import cuda_impl as cu
 
             with trace("experts_route"):
                 _, _, dense = cu.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale, dense=True)
             with trace("experts_dense_up"):
-                a = ops.linear(h, self.w_up.view(E * F, -1), act=self.act)
+                a = ops.linear(h, self.w_up.view(self.w_up.shape[0] * self.w_up.shape[1], -1), act=self.act, gated=self.gated)
                 cu.moe_scale(a, dense, E, F)
             with trace("experts_dense_down"):
                 return ops.linear(a, self.w_down, out_dtype=torch.float32)
         with trace("experts_route"):
             ids, wts = ops.moe_route(z, E, self.top, self.groups, self.keep, self.route_scale)
         with trace("experts_gather"):
-            return ops.moe_experts(h, ids, wts, self.w_up, self.w_down, self.act)
+            return ops.moe_experts(h, ids, wts, self.w_up, self.w_down, self.act, self.gated)

@@ -19,6 +19,7 @@ from ..engine.batch import BatchInput
 from .bedovik import BedovikLM, bedovik_spec, load_bedovik
 from .decoder import DecoderLM
 from .families import FAMILIES
+from .ninelix import NinelixLM, load_ninelix, ninelix_spec
 
 
 class PagedState:
@@ -33,7 +34,7 @@ class PagedState:
         bs = self.block_size
         self.blocks_per_seq = max(1, -(-capacity // bs))
         self.capacity = self.blocks_per_seq * bs
-        self.kv = self.core.make_cache(1 + self.B * self.blocks_per_seq, bs)
+        self.kv = self.core.make_cache(1 + self.B * self.blocks_per_seq, bs, max_seqs=self.B)   # sequence i keeps state slot i
         self.tables = [[1 + i * self.blocks_per_seq + j for j in range(self.blocks_per_seq)] for i in range(self.B)]
 
     def ensure(self, total_len: int):
@@ -41,7 +42,7 @@ class PagedState:
             return
         old_kv, old_bps = self.kv, self.blocks_per_seq
         self._alloc(max(total_len, 2 * self.capacity))
-        # copy the live blocks of every sequence into the enlarged cache
+        # copy the live blocks of every sequence (and, with them, the state slots) into the enlarged cache
         for i in range(self.B):
             src = 1 + i * old_bps
             dst = 1 + i * self.blocks_per_seq
@@ -90,7 +91,8 @@ class CausalLM(nn.Module):
         ctx = st.length
         st.ensure(ctx + S)
         ids = input_ids.tolist()
-        batch = BatchInput.build(ids, [ctx] * B, st.tables, st.block_size, core.device, max_blocks=st.blocks_per_seq)
+        batch = BatchInput.build(ids, [ctx] * B, st.tables, st.block_size, core.device, max_blocks=st.blocks_per_seq,
+                                 state_slots=list(range(B)) if getattr(core, "needs_state", False) else None)
         hidden = core.forward_hidden(batch, st.kv)
         if last_only:
             logits = core.logits(hidden.index_select(0, batch.last_idx))[:, :core.spec.vocab].reshape(B, 1, -1)
@@ -134,6 +136,20 @@ class BedovikForCausalLM(CausalLM):
         self.core.finalize()
 
 
+class NinelixForCausalLM(CausalLM):
+    """Native architecture (see models/ninelix.py): recurrent mixers and biased attention over a 32-bit residual stream
+    with post-normed sub-layers.  Same constructor and forward interface as the HF-shaped classes."""
+    family = "ninelix"
+    float32_on_cuda = True
+
+    def __init__(self, config, weights, fuse_parallel: bool = True):
+        nn.Module.__init__(self)
+        self.config = config
+        self.core = NinelixLM(ninelix_spec(config), weights.process_group, weights.device, weights.dtype)
+        load_ninelix(self.core, weights)
+        self.core.finalize()
+
+
 MODEL_REGISTRY = {
     "gptj": GPTJForCausalLM,
     "gpt_bigcode": GPTBigCodeForCausalLM,
@@ -141,4 +157,5 @@ MODEL_REGISTRY = {
     "opt": OPTForCausalLM,
     "llama": LlamaForCausalLM,
     "bedovik": BedovikForCausalLM,
+    "ninelix": NinelixForCausalLM,
 }

@@ -135,7 +135,7 @@ class DecoderLM(nn.Module):
         oracle path and head sizes the kernel does not cover keep 16."""
         return 64 if (self.device.type == "cuda" and self.d in (64, 128, 256)) else 16
 
-    def make_cache(self, num_blocks: int, block_size: int):
+    def make_cache(self, num_blocks: int, block_size: int, max_seqs=None):
         from ..engine.kv_cache import KVCache
 
         return KVCache(self.spec.n_layers, num_blocks, block_size, self.hkv, self.d, self.dtype, self.device)

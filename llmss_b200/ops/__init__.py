@@ -14,6 +14,8 @@ from typing import Optional
 import torch
 
 from . import reference as ref
+from .reference import (DECAY_HEAD, DECAY_TOKEN_CHANNEL, DECAY_TOKEN_HEAD, GATE_NONE, GATE_SIGMOID, GATE_SILU, UNARY_NEG_EXP,
+                        UNARY_TANH, distance_bias_table)
 from .reference import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_IDS, ACT_NONE, ACT_RELU, ACT_RELU2, ACT_SILU, NORM_DYT, NORM_LAYER,
                         NORM_RMS, ROPE_GPTJ, ROPE_NEOX, ROPE_NONE)
 
@@ -259,12 +261,75 @@ def moe_route(z, experts, top, groups, keep, route_scale):
     return ref.moe_route(z, experts, top, groups, keep, route_scale)
 
 
-def moe_experts(h, ids, wts, w_up, w_down, act):
+def moe_experts(h, ids, wts, w_up, w_down, act, gated: bool = False):
     if _cuda(h):
         from . import cuda_impl as cu
 
-        return cu.moe_experts(h, ids, wts, w_up, w_down, act)
-    return ref.moe_experts(h, ids, wts, w_up, w_down, act)
+        return cu.moe_experts(h, ids, wts, w_up, w_down, act, gated)
+    return ref.moe_experts(h, ids, wts, w_up, w_down, act, gated)
+
+
+# ----------------------------------------------------------------------------- recurrent layers, post-norm residual
+def _dispatch(name, probe, *args, **kw):
+    if _cuda(probe):
+        from . import cuda_impl as cu
+
+        return getattr(cu, name)(*args, **kw)
+    return getattr(ref, name)(*args, **kw)
+
+
+def embed_bigram(tokens, wte, table, mul_prev, mul_cur, buckets, batch, prev_state):
+    """Token embedding plus a hashed (previous token, token) embedding, 32-bit; see ops.reference.embed_bigram."""
+    return _dispatch("embed_bigram", wte, tokens, wte, table, mul_prev, mul_cur, buckets, batch, prev_state)
+
+
+def postnorm_residual(y, weight, eps, resid=None, y2=None, w_a=None, w_b=None, one_plus=True, out_dtype=None):
+    """RMS norm on a sub-layer's output (optionally the mean of two normed branches first), then the 32-bit residual
+    sum: the post-norm counterpart of norm_residual / dyt_residual."""
+    return _dispatch("postnorm_residual", y, y, weight, eps, resid, y2, w_a, w_b, one_plus, out_dtype)
+
+
+def token_shift(x, mu, batch, prev_state, out_dtype=None):
+    return _dispatch("token_shift", x, x, mu, batch, prev_state, out_dtype)
+
+
+def causal_conv(u, w, bias, act, batch, state):
+    return _dispatch("causal_conv", u, u, w, bias, act, batch, state)
+
+
+def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions, slot_mapping, k_cache, v_cache,
+                    out_dtype=None):
+    return _dispatch("qknorm_kv_write", qkv, qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions,
+                     slot_mapping, k_cache, v_cache, out_dtype)
+
+
+def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None):
+    """Causal paged attention with separate key / value sizes, a per-head distance bias table and an output gate."""
+    if _cuda(q):
+        from . import cuda_impl as cu
+
+        return cu.attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate, out_dtype)
+    return ref.attention_bias(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q, hq, hkv, dk, dv, scale,
+                              dist_bias, gate, out_dtype)
+
+
+def unary(x, op, out_dtype=None):
+    return _dispatch("unary", x, x, op, out_dtype)
+
+
+def ssm_dt(dt_raw, dt_bias, a_log):
+    return _dispatch("ssm_dt", dt_raw, dt_raw, dt_bias, a_log)
+
+
+def linear_scan(q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, dv, bonus=None, v_scale=None,
+                read_before=False):
+    """Gated linear recurrence (RWKV time mixing, lightning attention, state-space duality are parameter choices)."""
+    return _dispatch("linear_scan", v, q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, dv, bonus, v_scale,
+                     read_before)
+
+
+def gated_rmsnorm(o, gate, gate_act, weight, groups, eps, gate_first, skip_x=None, skip_d=None, out_dtype=None):
+    return _dispatch("gated_rmsnorm", o, o, gate, gate_act, weight, groups, eps, gate_first, skip_x, skip_d, out_dtype)
 
 
 def sample(logits, greedy, temperature, top_k, top_p, rng_state, vocab: Optional[int] = None, out=None):

@@ -114,7 +114,7 @@ _SIGS = {
     "llmss_moe_route": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                 c_void_p]),
     "llmss_moe_experts": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
-                                  c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "llmss_moe_count": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "llmss_moe_permute": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "llmss_moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),

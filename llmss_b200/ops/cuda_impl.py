@@ -535,16 +535,18 @@ def moe_route(z, experts, top, groups, keep, route_scale, dense: bool = False):
     return (ids, wts, dn) if dense else (ids, wts)
 
 
-def moe_experts(h, ids, wts, w_up, w_down, act):
+def moe_experts(h, ids, wts, w_up, w_down, act, gated: bool = False):
     lib = _lib.load()
     T, W, ldh = _rows2d(h)
     E, F, _ = w_up.shape
+    if gated:
+        F //= 2       # rows interleave (gate_f, up_f)
     top = ids.shape[1]
     assert w_up.is_contiguous() and w_down.is_contiguous() and h.dtype == w_up.dtype
     scratch = torch.empty(T, top, F, dtype=h.dtype, device=h.device)
     out = torch.empty(T, W, dtype=torch.float32, device=h.device)
     rc = lib.llmss_moe_experts(_ptr(h), ldh, _ptr(ids), _ptr(wts), _ptr(w_up), _ptr(w_down), w_down.stride(0), _ptr(scratch), _ptr(out),
-                               out.stride(0), T, W, F, top, act, _DT[h.dtype], _stream())
+                               out.stride(0), T, W, F, top, act, 1 if gated else 0, _DT[h.dtype], _stream())
     _lib.check(rc, "llmss_moe_experts")
     _count(2)
     return out
@@ -558,13 +560,15 @@ def moe_scale(a, dense, experts: int, ff: int):
     return a
 
 
-def moe_experts_grouped(h, ids, wts, w_up, w_down, act):
+def moe_experts_grouped(h, ids, wts, w_up, w_down, act, gated: bool = False):
     """Long prompts: sort the (token, expert) pairs by expert on the device and run every expert as one pair of tensor-core
     GEMMs over its contiguous rows -- top / experts of the dense form's FLOPs.  Reads the per-expert counts on the host (one
     small synchronising copy), so it is for prompt processing, not for graph-captured decode steps."""
     lib = _lib.load()
     T, W, ldh = _rows2d(h)
     E, F, _ = w_up.shape
+    if gated:
+        F //= 2
     top = ids.shape[1]
     P, dev = T * top, h.device
     counts = torch.empty(E, dtype=torch.int32, device=dev)
@@ -586,7 +590,7 @@ def moe_experts_grouped(h, ids, wts, w_up, w_down, act):
     y = torch.empty(P, W, dtype=torch.float32, device=dev)
     for e, (lo, c) in enumerate(zip(offs, cnt)):
         if c:
-            linear(xs[lo:lo + c], w_up[e], act=act, out=a[lo:lo + c])
+            linear(xs[lo:lo + c], w_up[e], act=act, gated=gated, out=a[lo:lo + c])
             linear(a[lo:lo + c], w_down[:, e * F:(e + 1) * F], out_dtype=torch.float32, out=y[lo:lo + c])
     out = torch.empty(T, W, dtype=torch.float32, device=dev)
     _lib.check(lib.llmss_moe_combine(_ptr(y), _ptr(inv), _ptr(wts), _ptr(out), out.stride(0), T, W, top, _stream()),

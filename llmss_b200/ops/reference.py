@@ -253,13 +253,19 @@ def moe_route(z, experts: int, top: int, groups: int, keep: int, route_scale: fl
     return idx.to(torch.int32), w
 
 
-def moe_experts(h, ids, wts, w_up, w_down, act: int):
+def moe_experts(h, ids, wts, w_up, w_down, act: int, gated: bool = False):
     """out[t] = sum_k wts[t, k] * W_down[ids[t, k]] act(W_up[ids[t, k]] h[t]);  w_up [E, F, W]; w_down [W, E * F] (the
-    experts' down matrices side by side); fp32 result."""
+    experts' down matrices side by side); fp32 result.  ``gated``: w_up is [E, 2 F, W] with rows interleaved (gate_0, up_0,
+    gate_1, ...) and the hidden activation is act(gate) * up."""
     T, W = h.shape
     E, F, _ = w_up.shape
     up = w_up.float()[ids.long()]                       # [T, top, F, W]
-    a = apply_act(torch.einsum("tkfw,tw->tkf", up, h.float()), act).to(h.dtype).float()
+    a = torch.einsum("tkfw,tw->tkf", up, h.float())
+    if gated:
+        F //= 2
+        a = (apply_act(a[..., 0::2], act) * a[..., 1::2]).to(h.dtype).float()
+    else:
+        a = apply_act(a, act).to(h.dtype).float()
     down = w_down.float().view(W, E, F).permute(1, 0, 2)[ids.long()]   # [T, top, W, F]
     return torch.einsum("tkwf,tkf,tk->tw", down, a, wts.float())
 
@@ -423,3 +429,230 @@ def sample_vocab_parallel(shards, greedy, temperature, top_k, top_p, rng_state, 
         pick = min(int((c <= u[b] * c[-1]).sum()), int(keep.sum()) - 1)
         toks[b] = si[pick]
     return toks
+
+
+# ----------------------------------------------------------------------------- recurrent layers, post-norm residual
+# Conventions shared by the ops below.  A packed batch holds B sequences; sequence i owns rows cu_q[i]:cu_q[i+1], has
+# seq_lens[i] tokens including those rows, and keeps its recurrent state in row state_slots[i] of every state tensor.
+# A sequence whose first row is its position 0 starts from a zero state whatever its slot holds, so slots need no
+# clearing when they are handed to a new sequence.  A slot < 0 marks an inert row (padding of a captured batch).
+GATE_NONE, GATE_SILU, GATE_SIGMOID = 0, 1, 2
+UNARY_TANH, UNARY_NEG_EXP = 0, 1
+DECAY_HEAD, DECAY_TOKEN_HEAD, DECAY_TOKEN_CHANNEL = 0, 1, 2
+
+
+def _seq_ranges(batch):
+    cu, lens, slots = batch.cu_q.tolist(), batch.seq_lens.tolist(), batch.state_slots.tolist()
+    for i in range(batch.num_seqs):
+        q0, q1 = cu[i], cu[i + 1]
+        if q1 > q0 and slots[i] >= 0:
+            yield q0, q1, lens[i] - (q1 - q0), slots[i]
+
+
+def _rms_div(x, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def embed_bigram(tokens, wte, table, mul_prev: int, mul_cur: int, buckets: int, batch, prev_state):
+    """x[t] = wte[tok_t] + table[(prev * mul_prev + tok_t * mul_cur) mod buckets] in 32-bit; a sequence's first token
+    takes row ``buckets``.  ``prev_state`` [slots] int32 keeps every sequence's last token between steps."""
+    tok = tokens.long()
+    x = F.embedding(tok, wte).float()
+    for q0, q1, ctx, slot in _seq_ranges(batch):
+        prev = torch.empty(q1 - q0, dtype=torch.long, device=tok.device)
+        prev[1:] = tok[q0:q1 - 1]
+        prev[0] = int(prev_state[slot]) if ctx > 0 else 0
+        rows = (prev * mul_prev + tok[q0:q1] * mul_cur) % buckets
+        if ctx == 0:
+            rows[0] = buckets
+        x[q0:q1] += F.embedding(rows, table).float()
+        prev_state[slot] = tok[q1 - 1].to(prev_state.dtype)
+    return x
+
+
+def postnorm_residual(y, weight, eps: float, resid=None, y2=None, w_a=None, w_b=None, one_plus: bool = True, out_dtype=None):
+    """Norm on a sub-layer's output, then the 32-bit residual sum.  n = rms_div(y) * (1 + weight) (``one_plus``) or
+    * weight; with ``y2`` the input is first 0.5 * (rms_div(y) * w_a + rms_div(y2) * w_b) (two branches side by side).
+    Returns (cast(resid + n), resid + n), or (cast(n), None) without a residual."""
+    v = y.float()
+    if y2 is not None:
+        v = 0.5 * (_rms_div(v, eps) * w_a.float() + _rms_div(y2.float(), eps) * w_b.float())
+    w = weight.float()
+    n = _rms_div(v, eps) * ((1.0 + w) if one_plus else w)
+    if resid is None:
+        return n.to(out_dtype or weight.dtype), None
+    r = resid.float() + n
+    return r.to(out_dtype or weight.dtype), r
+
+
+def token_shift(x, mu, batch, prev_state, out_dtype=None):
+    """mix[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] for every mixing vector mu[s] (x[-1] of a sequence = 0);
+    ``prev_state`` [slots, width] 32-bit carries each sequence's last row to its next step.  Returns [S, T, width]."""
+    xf = x.float()
+    prev = torch.zeros_like(xf)
+    for q0, q1, ctx, slot in _seq_ranges(batch):
+        prev[q0 + 1:q1] = xf[q0:q1 - 1]
+        if ctx > 0:
+            prev[q0] = prev_state[slot]
+        prev_state[slot] = xf[q1 - 1]
+    out = xf[None] + (prev - xf)[None] * mu.float()[:, None, :]
+    return out.to(out_dtype or x.dtype)
+
+
+def causal_conv(u, w, bias, act: int, batch, state):
+    """Short causal convolution over time per channel: y_t = sum_j w[:, j] u_(t - taps + 1 + j) (+ bias), then ``act``.
+    u [T, C] (a column view is fine), w [C, taps]; ``state`` [slots, taps - 1, C] 32-bit holds each sequence's last
+    taps - 1 inputs (zeros before its start).  32-bit result."""
+    T, C = u.shape
+    taps = w.shape[1]
+    wf, uf = w.float(), u.float()
+    y = torch.zeros(T, C, dtype=torch.float32, device=u.device)
+    for q0, q1, ctx, slot in _seq_ranges(batch):
+        hist = state[slot].float() if ctx > 0 and taps > 1 else torch.zeros(taps - 1, C, dtype=torch.float32, device=u.device)
+        full = torch.cat([hist, uf[q0:q1]])
+        for j in range(taps):
+            y[q0:q1] += wf[:, j] * full[j:j + q1 - q0]
+        if taps > 1:
+            state[slot] = full[full.shape[0] - (taps - 1):]
+    if bias is not None:
+        y = y + bias.float()
+    return apply_act(y, act)
+
+
+def qknorm_kv_write(qkv, hq: int, hkv: int, dk: int, dv: int, q_w, k_w, eps: float, temp_coef: float, temp_every: int,
+                    positions, slot_mapping, k_cache, v_cache, out_dtype=None):
+    """Per-head RMS norm of queries and keys (one plain weight of size dk each, shared by the heads), the query
+    temperature 1 + coef * ln(floor((p + 1) / every) + 1) at position p (coef = 0: none), and the append of k / v to
+    the paged cache (k_cache [blocks, hkv, bs, dk], v_cache [blocks, hkv, bs, dv]).  qkv [T, hq*dk + hkv*dk + hkv*dv]
+    32-bit.  Returns the queries [T, hq * dk]."""
+    T = qkv.shape[0]
+    q = _rms_div(qkv[:, :hq * dk].float().view(T, hq, dk), eps) * q_w.float()
+    k = _rms_div(qkv[:, hq * dk:(hq + hkv) * dk].float().view(T, hkv, dk), eps) * k_w.float()
+    v = qkv[:, (hq + hkv) * dk:].float().view(T, hkv, dv)
+    if temp_coef != 0.0:
+        temp = 1.0 + temp_coef * torch.log(torch.div(positions.long() + 1, temp_every, rounding_mode="floor").float() + 1.0)
+        q = q * temp[:, None, None]
+    bs = k_cache.shape[2]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    k_cache[slots // bs, :, slots % bs, :] = k[valid].to(k_cache.dtype)
+    v_cache[slots // bs, :, slots % bs, :] = v[valid].to(v_cache.dtype)
+    return q.reshape(T, hq * dk).to(out_dtype or k_cache.dtype)
+
+
+def distance_bias_table(rel, max_distance: int):
+    """Learned distance bias as a dense table: out[h, n] = rel[bucket(n), h] for n = 0 .. max_distance (larger distances
+    use the last column).  Buckets: n itself below half of the B rows, then logarithmic up to ``max_distance``."""
+    B, H = rel.shape
+    half = B // 2
+    cols = []
+    for n in range(max_distance + 1):
+        b = n if n < half else min(B - 1, half + int(math.floor(math.log(n / half) / math.log(max_distance / half) * (B - half))))
+        cols.append(rel[b].float())
+    return torch.stack(cols, dim=1).contiguous()
+
+
+def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, hkv: int, dk: int, dv: int, scale: float,
+                   dist_bias, gate=None, out_dtype=None):
+    """Causal softmax attention over the paged cache with key size dk, value size dv, grouped heads, an additive bias
+    dist_bias[h, min(i - j, last)] per head and distance, and an optional per-head output gate sigmoid(gate[t, h])."""
+    T = q.shape[0]
+    bs, g = k_cache.shape[2], hq // hkv
+    out = torch.zeros(T, hq, dv, dtype=torch.float32, device=q.device)
+    cu, lens = cu_q.tolist(), seq_lens.tolist()
+    last = dist_bias.shape[1] - 1
+    for i, L in enumerate(lens):
+        q0, q1 = cu[i], cu[i + 1]
+        ql = q1 - q0
+        if ql == 0 or L == 0:
+            continue
+        nb = (L + bs - 1) // bs
+        blocks = block_tables[i, :nb].long()
+        k = k_cache[blocks].permute(1, 0, 2, 3).reshape(hkv, nb * bs, dk)[:, :L].float().repeat_interleave(g, dim=0)
+        v = v_cache[blocks].permute(1, 0, 2, 3).reshape(hkv, nb * bs, dv)[:, :L].float().repeat_interleave(g, dim=0)
+        qi = q[q0:q1].float().view(ql, hq, dk).permute(1, 0, 2)
+        s = torch.matmul(qi, k.transpose(1, 2)) * scale
+        qpos = torch.arange(L - ql, L, device=q.device)[:, None]
+        kpos = torch.arange(L, device=q.device)[None, :]
+        dist = (qpos - kpos).clamp(min=0, max=last)
+        s = s + dist_bias.float()[:, dist.reshape(-1)].view(hq, ql, L)
+        s = s.masked_fill(kpos > qpos, float("-inf"))
+        out[q0:q1] = torch.matmul(torch.softmax(s, dim=-1), v).permute(1, 0, 2)
+    if gate is not None:
+        out = out * torch.sigmoid(gate.float())[:, :, None]
+    return out.reshape(T, hq * dv).to(out_dtype or q.dtype)
+
+
+def unary(x, op: int, out_dtype=None):
+    y = torch.tanh(x.float()) if op == UNARY_TANH else -torch.exp(x.float())
+    return y.to(out_dtype or x.dtype)
+
+
+def ssm_dt(dt_raw, dt_bias, a_log):
+    """Step sizes of a selective state-space layer: dt = softplus(dt_raw + dt_bias) (no clamp) and the log of the
+    per-step decay, -exp(a_log) * dt; both [T, heads] 32-bit."""
+    dt = F.softplus(dt_raw.float() + dt_bias.float(), threshold=30.0)
+    return dt, -torch.exp(a_log.float()) * dt
+
+
+def linear_scan(q, k, v, decay, decay_kind: int, batch, state, heads: int, qk_heads: int, dk: int, dv: int, bonus=None,
+                v_scale=None, read_before: bool = False):
+    """Gated linear recurrence per head, state S [dk, dv] in 32-bit:
+         S_t = diag(a_t) S_(t-1) + k_t (c_t v_t)^T
+         o_t = S_t^T q_t                                   (read_before = False)
+         o_t = (S_(t-1) + diag(bonus) k_t (c_t v_t)^T)^T q_t     (read_before = True)
+    q, k [T, qk_heads * dk] (head h reads q/k head h // (heads / qk_heads)), v [T, heads * dv], c = v_scale [T, heads] or 1.
+    a_t: DECAY_HEAD -> decay[h]; DECAY_TOKEN_HEAD -> exp(decay[t, h]); DECAY_TOKEN_CHANNEL -> exp(decay[t, h * dk + i]).
+    ``state`` [slots, heads, dk, dv].  Returns o [T, heads * dv] 32-bit."""
+    T = v.shape[0]
+    rep = heads // qk_heads
+    qf = q.float().view(T, qk_heads, dk).repeat_interleave(rep, dim=1)
+    kf = k.float().view(T, qk_heads, dk).repeat_interleave(rep, dim=1)
+    vf = v.float().view(T, heads, dv)
+    if v_scale is not None:
+        vf = vf * v_scale.float()[:, :, None]
+    if decay_kind == DECAY_HEAD:
+        a = decay.float().view(1, heads, 1).expand(T, heads, dk)
+    elif decay_kind == DECAY_TOKEN_HEAD:
+        a = torch.exp(decay.float()).view(T, heads, 1).expand(T, heads, dk)
+    else:
+        a = torch.exp(decay.float()).view(T, heads, dk)
+    out = torch.zeros(T, heads, dv, dtype=torch.float32, device=v.device)
+    for q0, q1, ctx, slot in _seq_ranges(batch):
+        S = state[slot].float().clone() if ctx > 0 else torch.zeros(heads, dk, dv, dtype=torch.float32, device=v.device)
+        for t in range(q0, q1):
+            kv = kf[t][:, :, None] * vf[t][:, None, :]
+            if read_before:
+                R = S + (bonus.float()[:, :, None] * kv if bonus is not None else 0.0)
+                S = a[t][:, :, None] * S + kv
+            else:
+                S = a[t][:, :, None] * S + kv
+                R = S
+            out[t] = torch.einsum("hkv,hk->hv", R, qf[t])
+        state[slot] = S
+    return out.reshape(T, heads * dv)
+
+
+def gated_rmsnorm(o, gate, gate_act: int, weight, groups: int, eps: float, gate_first: bool, skip_x=None, skip_d=None,
+                  out_dtype=None):
+    """Output stage of the recurrent mixers.  y = o (+ skip_d[h] * skip_x, head h = equal slices of the row); the row
+    is cut into ``groups`` equal parts, each divided by its own root mean square, times ``weight``; the gate
+    act(gate) multiplies before (``gate_first``) or after the norm."""
+    T, C = o.shape
+    y = o.float()
+    if skip_x is not None:
+        H = skip_d.numel()
+        y = y + (skip_x.float().view(T, H, C // H) * skip_d.float()[None, :, None]).reshape(T, C)
+    g = None
+    if gate is not None and gate_act != GATE_NONE:
+        g = F.silu(gate.float()) if gate_act == GATE_SILU else torch.sigmoid(gate.float())
+    elif gate is not None:
+        g = gate.float()
+    if g is not None and gate_first:
+        y = y * g
+    y = _rms_div(y.view(T, groups, C // groups), eps).reshape(T, C)
+    if weight is not None:
+        y = y * weight.float()
+    if g is not None and not gate_first:
+        y = y * g
+    return y.to(out_dtype or o.dtype)
