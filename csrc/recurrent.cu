@@ -1,0 +1,468 @@
+// Kernels of recurrent token mixers over a packed batch, and of the post-normed 32-bit residual stream.
+//
+// Batch convention (all kernels): sequence b owns rows cu_q[b] .. cu_q[b+1] of the packed batch, holds seq_lens[b] tokens
+// including them, and keeps what it carries from step to step in row state_slots[b] of each state tensor.  A sequence
+// whose first row is its position 0 starts from zeros whatever the slot holds (slots change hands uncleared); a slot < 0
+// is an inert row of a padded batch and is skipped.  State rows are read and written by ONE block per (sequence, slice):
+// the block that reads a slot's old state is the block that writes its new one, so a step needs no ordering between
+// blocks even when a portion is many rows long.
+//
+//   embed_bigram      x = wte[tok] + table[(prev * mul_prev + tok * mul_cur) mod buckets]   (row `buckets` for a first token)
+//   postnorm_residual r' = r + rms_div(y) * (1 + w)     (optionally y = mean of two normed branches)  -> (cast(r'), r')
+//   token_shift       mix_s = x + (x_prev - x) * mu_s   for S mixing vectors at once
+//   causal_conv       y_t = act(sum_j w[:, j] u_(t - taps + 1 + j) + b)  per channel, tails kept per sequence
+//   unary / ssm_dt    tanh, -exp;  dt = softplus(raw + bias), log decay = -exp(A_log) dt
+//   linear_scan       S_t = diag(a_t) S_(t-1) + k_t (c_t v_t)^T ;  o_t = S_t^T q_t   or   (S_(t-1) + diag(u) k_t v_t^T)^T q_t
+//   gated_rmsnorm     y = o (+ D x); gate before or after; rms_div in equal groups; times weight
+//
+// Everything here computes in 32-bit: states, decays, exponentials, norms and the residual sum.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {   // red: >= 32 floats of shared memory
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+struct Seq {
+  int q0, ql, ctx, slot;
+};
+__device__ __forceinline__ Seq seq_of(const int* cu_q, const int* seq_lens, const int* slots, int b) {
+  Seq s;
+  s.q0 = cu_q[b];
+  s.ql = cu_q[b + 1] - s.q0;
+  s.ctx = seq_lens[b] - s.ql;
+  s.slot = slots[b];
+  if (s.slot < 0 || s.ctx < 0) s.ql = 0;
+  return s;
+}
+
+// ------------------------------------------------------------------------------------------------ embed_bigram
+// grid (B, row lanes); block (b, 0) owns row 0 of the sequence and with it the slot's previous-token entry
+template <typename T>
+__global__ void __launch_bounds__(128) embed_bigram_kernel(const int* __restrict__ tokens, const T* __restrict__ wte,
+                                                           const T* __restrict__ table, float* __restrict__ out, int W, int vocab,
+                                                           long long mul_prev, long long mul_cur, int buckets,
+                                                           const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                                                           const int* __restrict__ slots, int* __restrict__ prev_state) {
+  const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
+  for (int j = blockIdx.y; j < s.ql; j += gridDim.y) {
+    const int t = s.q0 + j;
+    const int tok = min(max(tokens[t], 0), vocab - 1);
+    int row;
+    if (j == 0 && s.ctx == 0) row = buckets;
+    else {
+      const long long prev = j > 0 ? tokens[t - 1] : prev_state[s.slot];
+      row = (int)((prev * mul_prev + (long long)tok * mul_cur) % buckets);
+      if (row < 0) row += buckets;
+    }
+    const T* a = wte + (int64_t)tok * W;
+    const T* b = table + (int64_t)row * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) out[(int64_t)t * W + c] = to_f32(a[c]) + to_f32(b[c]);
+  }
+  if (blockIdx.y == 0 && s.ql > 0) {
+    __syncthreads();   // row 0 has read the old entry
+    if (threadIdx.x == 0) prev_state[s.slot] = tokens[s.q0 + s.ql - 1];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ postnorm_residual
+template <typename T>
+__global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ y2,
+                                                       int64_t ldy2, const float* __restrict__ w_a, const float* __restrict__ w_b,
+                                                       const float* __restrict__ weight, const float* __restrict__ resid,
+                                                       int64_t ldr, float* __restrict__ new_resid, T* __restrict__ out, int W,
+                                                       float eps, int one_plus) {
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const float* yr = y + t * ldy;
+  const float* y2r = y2 != nullptr ? y2 + t * ldy2 : nullptr;
+  float ra = 0.f, rb = 0.f;
+  if (y2r != nullptr) {
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { sa = fmaf(yr[c], yr[c], sa); sb = fmaf(y2r[c], y2r[c], sb); }
+    ra = rsqrtf(block_sum(sa, red) / W + eps);
+    rb = rsqrtf(block_sum(sb, red) / W + eps);
+  }
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = y2r != nullptr ? 0.5f * (yr[c] * ra * w_a[c] + y2r[c] * rb * w_b[c]) : yr[c];
+    ss = fmaf(v, v, ss);
+  }
+  const float r = rsqrtf(block_sum(ss, red) / W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = y2r != nullptr ? 0.5f * (yr[c] * ra * w_a[c] + y2r[c] * rb * w_b[c]) : yr[c];
+    float n = v * r * (one_plus ? 1.f + weight[c] : weight[c]);
+    if (resid != nullptr) {
+      n += resid[t * ldr + c];
+      new_resid[t * W + c] = n;
+    }
+    out[t * W + c] = from_f32<T>(n);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ token_shift
+template <typename T>
+__global__ void __launch_bounds__(128) token_shift_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ mu,
+                                                          int S, T* __restrict__ out, int64_t Ttot, int W,
+                                                          const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                                                          const int* __restrict__ slots, float* __restrict__ prev_state) {
+  const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
+  for (int j = blockIdx.y; j < s.ql; j += gridDim.y) {
+    const int64_t t = s.q0 + j;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float cur = x[t * ldx + c];
+      const float prev = j > 0 ? x[(t - 1) * ldx + c] : (s.ctx > 0 ? prev_state[(int64_t)s.slot * W + c] : 0.f);
+      const float d = prev - cur;
+      for (int k = 0; k < S; ++k) out[((int64_t)k * Ttot + t) * W + c] = from_f32<T>(fmaf(d, mu[(int64_t)k * W + c], cur));
+      // the thread that read column c of the old row is the one that replaces it
+      if (j == 0 && blockIdx.y == 0) prev_state[(int64_t)s.slot * W + c] = x[(int64_t)(s.q0 + s.ql - 1) * ldx + c];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ causal_conv
+constexpr int kConvChunk = 64, kMaxTaps = 8;
+
+// grid (B, ceil(C / 128), token chunks); thread = channel; chunk 0 of a sequence reads and replaces the slot's tail
+__global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restrict__ u, int64_t ldu, const float* __restrict__ w,
+                                                          const float* __restrict__ bias, float* __restrict__ out, int C, int taps,
+                                                          int act, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                                                          const int* __restrict__ slots, float* __restrict__ state) {
+  const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
+  const int c = blockIdx.y * 128 + threadIdx.x;
+  if (c >= C) return;
+  const int hist = taps - 1;
+  float wt[kMaxTaps], win[kMaxTaps], old[kMaxTaps];
+#pragma unroll
+  for (int i = 0; i < kMaxTaps; ++i) { wt[i] = i < taps ? w[(int64_t)c * taps + i] : 0.f; old[i] = 0.f; }
+  const float bv = bias != nullptr ? bias[c] : 0.f;
+  float* st = state != nullptr && s.slot >= 0 ? state + ((int64_t)s.slot * hist) * C + c : nullptr;
+  for (int z = blockIdx.z; z * kConvChunk < s.ql; z += gridDim.z) {
+    const int j0 = z * kConvChunk, j1 = min(s.ql, j0 + kConvChunk);
+    if (z == 0 && st != nullptr && s.ctx > 0) {
+#pragma unroll
+      for (int i = 0; i < kMaxTaps; ++i) if (i < hist) old[i] = st[(int64_t)i * C];
+    }
+    // window = inputs j0 - hist .. j0 - 1 (win[i] is input j0 - hist + i); only chunk 0 reaches before the step's first row
+#pragma unroll
+    for (int i = 0; i < kMaxTaps; ++i) {
+      const int jj = j0 - hist + i;
+      win[i] = i >= hist ? 0.f : (jj >= 0 ? u[(int64_t)(s.q0 + jj) * ldu + c] : old[i]);
+    }
+    for (int j = j0; j < j1; ++j) {
+      const float cur = u[(int64_t)(s.q0 + j) * ldu + c];
+      float acc = bv;
+#pragma unroll
+      for (int i = 0; i < kMaxTaps; ++i) if (i < taps) acc = fmaf(wt[i], i < hist ? win[i] : cur, acc);
+#pragma unroll
+      for (int i = 0; i < kMaxTaps - 1; ++i) win[i] = i + 1 < hist ? win[i + 1] : cur;
+      out[(int64_t)(s.q0 + j) * C + c] = act_exact(acc, act);
+    }
+    if (z == 0 && st != nullptr) {
+      // new tail: inputs ql - hist .. ql - 1; those before this step's first row come from the old tail
+#pragma unroll
+      for (int i = 0; i < kMaxTaps; ++i) {
+        if (i >= hist) continue;
+        const int jj = s.ql - hist + i;
+        float v;
+        if (jj >= 0) v = u[(int64_t)(s.q0 + jj) * ldu + c];
+        else {
+          v = 0.f;
+#pragma unroll
+          for (int k = 0; k < kMaxTaps; ++k) if (k == i + s.ql) v = old[k];
+        }
+        st[(int64_t)i * C] = v;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ elementwise
+template <typename TO>
+__global__ void __launch_bounds__(256) unary_kernel(const float* __restrict__ x, int64_t ldx, TO* __restrict__ out, int64_t n,
+                                                    int cols, int op) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = x[(i / cols) * ldx + i % cols];
+    out[i] = from_f32<TO>(op == 0 ? tanhf(v) : -expf(v));
+  }
+}
+
+__global__ void __launch_bounds__(256) ssm_dt_kernel(const float* __restrict__ raw, int64_t ldr, const float* __restrict__ dt_bias,
+                                                     const float* __restrict__ a_log, float* __restrict__ dt,
+                                                     float* __restrict__ logdecay, int64_t n, int H) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int h = (int)(i % H);
+    const float v = raw[(i / H) * ldr + h] + dt_bias[h];
+    const float d = v > 30.f ? v : log1pf(expf(v));
+    dt[i] = d;
+    logdecay[i] = -expf(a_log[h]) * d;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ linear_scan
+// One block per (sequence, head, slice of value channels).  Thread (j, r) keeps rows [r * 16, r * 16 + 16) of column j
+// of the state in registers (thread index = j * R + r, R a power of two, so the R partial dot products of an output meet
+// in one warp shuffle).  Tokens are staged 16 at a time through shared memory: q, k, per-channel decays, scaled values.
+// The state lies in memory column-major per head ([dv][dk]: a thread's 16 rows are contiguous).
+constexpr int KPT = 16, TCH = 16;
+struct ScanArgs {
+  const float* q; int64_t ldq;
+  const float* k; int64_t ldk;
+  const float* v; int64_t ldv;
+  const float* decay; int64_t ldd;     // kind 0: [H] decays; 1: [T, H] log decays; 2: [T, H * dk] log decays
+  const float* bonus;                  // [H, dk] or null
+  const float* vscale; int64_t ldvs;   // [T, H] or null
+  float* out;                          // [T, H * dv]
+  float* state;                        // [slots, H, dv, dk]
+  const int* cu_q; const int* seq_lens; const int* slots;
+  int H, rep, dk, dv, dvt, R;
+};
+
+template <bool READ_BEFORE, int KIND>
+__global__ void __launch_bounds__(1024) linear_scan_kernel(ScanArgs a) {
+  extern __shared__ float sm[];
+  const Seq s = seq_of(a.cu_q, a.seq_lens, a.slots, blockIdx.x);
+  if (s.ql == 0) return;
+  const int h = blockIdx.y, j0 = blockIdx.z * a.dvt;
+  const int nj = min(a.dvt, a.dv - j0);
+  const int dk = a.dk, R = a.R;
+  const int jl = threadIdx.x / R, r = threadIdx.x % R;
+  const bool live = jl < nj;
+  const int j = j0 + jl, i0 = r * KPT;
+  float* qs = sm;                       // [TCH][dk]
+  float* ks = qs + TCH * dk;            // [TCH][dk]
+  float* as = ks + TCH * dk;            // [TCH][dk] (kind 2) or [TCH] (kind 1)
+  float* vs = as + (KIND == 2 ? TCH * dk : TCH);   // [TCH][dvt]
+  float S[KPT], u[KPT];
+  float* sp = a.state + (((int64_t)s.slot * a.H + h) * a.dv + (live ? j : 0)) * dk;
+#pragma unroll
+  for (int ii = 0; ii < KPT; ++ii) {
+    const int i = i0 + ii;
+    S[ii] = (live && s.ctx > 0 && i < dk) ? sp[i] : 0.f;
+    u[ii] = (READ_BEFORE && a.bonus != nullptr && i < dk) ? a.bonus[(int64_t)h * dk + i] : 0.f;
+  }
+  const float a_const = KIND == 0 ? a.decay[h] : 0.f;
+  const int hq = h / a.rep;
+  for (int c0 = 0; c0 < s.ql; c0 += TCH) {
+    const int nt = min(TCH, s.ql - c0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * dk; idx += blockDim.x) {
+      const int tt = idx / dk, i = idx % dk;
+      const int64_t t = s.q0 + c0 + tt;
+      qs[tt * dk + i] = a.q[t * a.ldq + (int64_t)hq * dk + i];
+      ks[tt * dk + i] = a.k[t * a.ldk + (int64_t)hq * dk + i];
+      if (KIND == 2) as[tt * dk + i] = expf(a.decay[t * a.ldd + (int64_t)h * dk + i]);
+    }
+    if (KIND == 1) for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) as[tt] = expf(a.decay[(int64_t)(s.q0 + c0 + tt) * a.ldd + h]);
+    for (int idx = threadIdx.x; idx < nt * nj; idx += blockDim.x) {
+      const int tt = idx / nj, jj = idx % nj;
+      const int64_t t = s.q0 + c0 + tt;
+      float val = a.v[t * a.ldv + (int64_t)h * a.dv + j0 + jj];
+      if (a.vscale != nullptr) val *= a.vscale[t * a.ldvs + h];
+      vs[tt * a.dvt + jj] = val;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vj = live ? vs[tt * a.dvt + jl] : 0.f;
+      const float at = KIND == 1 ? as[tt] : a_const;
+      float acc = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < KPT; ++ii) {
+        const int i = i0 + ii;
+        if (i < dk) {
+          const float kv = ks[tt * dk + i] * vj;
+          const float dec = KIND == 2 ? as[tt * dk + i] : at;
+          if (READ_BEFORE) {
+            acc = fmaf(qs[tt * dk + i], fmaf(u[ii], kv, S[ii]), acc);
+            S[ii] = fmaf(dec, S[ii], kv);
+          } else {
+            S[ii] = fmaf(dec, S[ii], kv);
+            acc = fmaf(qs[tt * dk + i], S[ii], acc);
+          }
+        }
+      }
+      for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && r == 0) a.out[(int64_t)(s.q0 + c0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = acc;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int ii = 0; ii < KPT; ++ii) if (i0 + ii < dk) sp[i0 + ii] = S[ii];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gated_rmsnorm
+struct GnArgs {
+  const float* o; int64_t ldo;
+  const float* gate; int64_t ldg;
+  const float* weight;
+  const float* skip_x; int64_t ldx;
+  const float* skip_d;
+  int C, groups, H, gate_act, gate_first;
+  float eps;
+};
+__device__ __forceinline__ float gate_fn(float g, int kind) {
+  if (kind == 1) return g / (1.f + expf(-g));
+  if (kind == 2) return 1.f / (1.f + expf(-g));
+  return g;
+}
+__device__ __forceinline__ float gn_value(const GnArgs& a, int64_t t, int c) {
+  float v = a.o[t * a.ldo + c];
+  if (a.skip_x != nullptr) v = fmaf(a.skip_d[c / (a.C / a.H)], a.skip_x[t * a.ldx + c], v);
+  if (a.gate != nullptr && a.gate_first) v *= gate_fn(a.gate[t * a.ldg + c], a.gate_act);
+  return v;
+}
+// one block per row; a warp per group while there are at least as many groups as warps, else the block per group
+template <typename T>
+__global__ void __launch_bounds__(256) gated_rmsnorm_kernel(GnArgs a, T* __restrict__ out) {
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const int gs = a.C / a.groups, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const bool per_warp = a.groups >= nw;
+  for (int g = per_warp ? warp : 0; g < a.groups; g += per_warp ? nw : 1) {
+    float ss = 0.f;
+    for (int c = per_warp ? lane : threadIdx.x; c < gs; c += per_warp ? 32 : blockDim.x) {
+      const float v = gn_value(a, t, g * gs + c);
+      ss = fmaf(v, v, ss);
+    }
+    ss = per_warp ? warp_sum(ss) : block_sum(ss, red);
+    const float r = rsqrtf(ss / gs + a.eps);
+    for (int c = per_warp ? lane : threadIdx.x; c < gs; c += per_warp ? 32 : blockDim.x) {
+      const int cc = g * gs + c;
+      float v = gn_value(a, t, cc) * r;
+      if (a.weight != nullptr) v *= a.weight[cc];
+      if (a.gate != nullptr && !a.gate_first) v *= gate_fn(a.gate[t * a.ldg + cc], a.gate_act);
+      out[t * a.C + cc] = from_f32<T>(v);
+    }
+  }
+}
+
+int grid_for(int64_t n) {
+  const int64_t b = (n + 255) / 256;
+  return (int)(b < 148 * 8 ? b : 148 * 8);
+}
+
+int pow2_at_least(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
+}  // namespace
+
+LLMSS_API int llmss_embed_bigram(const int* tokens, const void* wte, const void* table, float* out, int T_, int W, int vocab,
+                                 int64_t mul_prev, int64_t mul_cur, int buckets, const int* cu_q, const int* seq_lens,
+                                 const int* slots, int B, int max_q, int* prev_state, int dtype, cudaStream_t stream) {
+  if (B <= 0 || T_ <= 0) return 0;
+  const dim3 grid(B, max(1, min(max_q, 256)));
+  LLMSS_BY_DTYPE(dtype, (embed_bigram_kernel<T><<<grid, 128, 0, stream>>>(tokens, (const T*)wte, (const T*)table, out, W, vocab, mul_prev,
+                                                                          mul_cur, buckets, cu_q, seq_lens, slots, prev_state)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_postnorm_residual(const float* y, int64_t ldy, const float* y2, int64_t ldy2, const float* w_a, const float* w_b,
+                                      const float* weight, const float* resid, int64_t ldr, float* new_resid, void* out, int T_,
+                                      int W, float eps, int one_plus, int dtype, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  LLMSS_REQUIRE(y2 == nullptr || (w_a != nullptr && w_b != nullptr), "postnorm_residual: two branches need two weights");
+  LLMSS_BY_DTYPE(dtype, (postnorm_kernel<T><<<T_, 256, 0, stream>>>(y, ldy, y2, ldy2, w_a, w_b, weight, resid, ldr, new_resid, (T*)out, W,
+                                                                    eps, one_plus)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_token_shift(const float* x, int64_t ldx, const float* mu, int S, void* out, int T_, int W, const int* cu_q,
+                                const int* seq_lens, const int* slots, int B, int max_q, float* prev_state, int dtype,
+                                cudaStream_t stream) {
+  if (B <= 0 || T_ <= 0) return 0;
+  const dim3 grid(B, max(1, min(max_q, 256)));
+  LLMSS_BY_DTYPE(dtype, (token_shift_kernel<T><<<grid, 128, 0, stream>>>(x, ldx, mu, S, (T*)out, (int64_t)T_, W, cu_q, seq_lens, slots,
+                                                                         prev_state)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_causal_conv(const float* u, int64_t ldu, const float* w, const float* bias, float* out, int T_, int C, int taps,
+                                int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state,
+                                cudaStream_t stream) {
+  LLMSS_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal_conv: %d taps (1..%d)", taps, kMaxTaps);
+  LLMSS_REQUIRE(taps == 1 || state != nullptr, "causal_conv: more than one tap needs a state");
+  if (B <= 0 || T_ <= 0) return 0;
+  const dim3 grid(B, (C + 127) / 128, max(1, min((max_q + kConvChunk - 1) / kConvChunk, 64)));
+  causal_conv_kernel<<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_unary_f32(const float* x, int64_t ldx, void* out, int rows, int cols, int op, int out_dtype, cudaStream_t stream) {
+  const int64_t n = (int64_t)rows * cols;
+  if (n <= 0) return 0;
+  LLMSS_BY_DTYPE(out_dtype, (unary_kernel<T><<<grid_for(n), 256, 0, stream>>>(x, ldx, (T*)out, n, cols, op)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_ssm_dt(const float* raw, int64_t ldr, const float* dt_bias, const float* a_log, float* dt, float* logdecay,
+                           int T_, int H, cudaStream_t stream) {
+  const int64_t n = (int64_t)T_ * H;
+  if (n <= 0) return 0;
+  ssm_dt_kernel<<<grid_for(n), 256, 0, stream>>>(raw, ldr, dt_bias, a_log, dt, logdecay, n, H);
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                                const float* decay, int64_t ldd, int decay_kind, const float* bonus, const float* vscale,
+                                int64_t ldvs, float* out, float* state, const int* cu_q, const int* seq_lens, const int* slots,
+                                int B, int heads, int qk_heads, int dk, int dv, int read_before, cudaStream_t stream) {
+  LLMSS_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "linear_scan: %d heads over %d q/k heads", heads, qk_heads);
+  LLMSS_REQUIRE(dk > 0 && dk <= 32 * KPT, "linear_scan: key size %d (at most %d)", dk, 32 * KPT);
+  LLMSS_REQUIRE(decay_kind >= 0 && decay_kind <= 2, "linear_scan: decay kind %d", decay_kind);
+  if (B <= 0) return 0;
+  ScanArgs a;
+  a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.decay = decay; a.ldd = ldd; a.bonus = bonus;
+  a.vscale = vscale; a.ldvs = ldvs; a.out = out; a.state = state; a.cu_q = cu_q; a.seq_lens = seq_lens; a.slots = slots;
+  a.H = heads; a.rep = heads / qk_heads; a.dk = dk; a.dv = dv;
+  a.R = pow2_at_least((dk + KPT - 1) / KPT);
+  a.dvt = min(dv, 1024 / a.R);
+  const int threads = ((a.dvt * a.R + 31) / 32) * 32;
+  const size_t smem = sizeof(float) * ((size_t)TCH * dk * 2 + (decay_kind == 2 ? (size_t)TCH * dk : TCH) + (size_t)TCH * a.dvt);
+  const dim3 grid(B, heads, (dv + a.dvt - 1) / a.dvt);
+#define LLMSS_SCAN(RB, KIND)                                                                   \
+  do {                                                                                         \
+    static PerDeviceSmem g;                                                                    \
+    LLMSS_CHECK_CUDA(g.ensure(linear_scan_kernel<RB, KIND>, (int)smem));                       \
+    linear_scan_kernel<RB, KIND><<<grid, threads, smem, stream>>>(a);                          \
+  } while (0)
+  if (read_before) {
+    if (decay_kind == 0) LLMSS_SCAN(true, 0); else if (decay_kind == 1) LLMSS_SCAN(true, 1); else LLMSS_SCAN(true, 2);
+  } else {
+    if (decay_kind == 0) LLMSS_SCAN(false, 0); else if (decay_kind == 1) LLMSS_SCAN(false, 1); else LLMSS_SCAN(false, 2);
+  }
+#undef LLMSS_SCAN
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_gated_rmsnorm(const float* o, int64_t ldo, const float* gate, int64_t ldg, int gate_act, const float* weight,
+                                  int groups, float eps, int gate_first, const float* skip_x, int64_t ldx, const float* skip_d,
+                                  int H, void* out, int T_, int C, int dtype, cudaStream_t stream) {
+  LLMSS_REQUIRE(groups > 0 && C % groups == 0, "gated_rmsnorm: %d channels in %d groups", C, groups);
+  LLMSS_REQUIRE(skip_x == nullptr || (skip_d != nullptr && H > 0 && C % H == 0), "gated_rmsnorm: skip needs one factor per head");
+  if (T_ <= 0) return 0;
+  GnArgs a;
+  a.o = o; a.ldo = ldo; a.gate = gate; a.ldg = ldg; a.weight = weight; a.skip_x = skip_x; a.ldx = ldx; a.skip_d = skip_d;
+  a.C = C; a.groups = groups; a.H = H > 0 ? H : 1; a.gate_act = gate_act; a.gate_first = gate_first; a.eps = eps;
+  LLMSS_BY_DTYPE(dtype, (gated_rmsnorm_kernel<T><<<T_, 256, 0, stream>>>(a, (T*)out)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -267,6 +267,38 @@ int llmss_sample(const float* logits, int64_t ld, int B, int vocab, const int* g
                  const int* top_k, const float* top_p, uint32_t* rng_state, int* out_tokens,
                  long long* out_tokens64, llmss_stream_t stream);
 
+/* ---- recurrent token mixers and the post-normed 32-bit residual stream (csrc/recurrent.cu, csrc/attn_bias.cu).
+ * Batch convention: sequence b owns rows cu_q[b]..cu_q[b+1], holds seq_lens[b] tokens including them, and keeps its state
+ * in row slots[b] of every state tensor (slot < 0: inert row).  A sequence at position 0 starts from zeros. */
+int llmss_embed_bigram(const int* tokens, const void* wte, const void* table, float* out, int T, int W, int vocab, int64_t mul_prev,
+                       int64_t mul_cur, int buckets, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q,
+                       int* prev_state, int dtype, llmss_stream_t stream);
+int llmss_postnorm_residual(const float* y, int64_t ldy, const float* y2, int64_t ldy2, const float* w_a, const float* w_b,
+                            const float* weight, const float* resid, int64_t ldr, float* new_resid, void* out, int T, int W,
+                            float eps, int one_plus, int dtype, llmss_stream_t stream);
+int llmss_token_shift(const float* x, int64_t ldx, const float* mu, int S, void* out, int T, int W, const int* cu_q,
+                      const int* seq_lens, const int* slots, int B, int max_q, float* prev_state, int dtype, llmss_stream_t stream);
+int llmss_causal_conv(const float* u, int64_t ldu, const float* w, const float* bias, float* out, int T, int C, int taps, int act,
+                      const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state, llmss_stream_t stream);
+int llmss_unary_f32(const float* x, int64_t ldx, void* out, int rows, int cols, int op, int out_dtype, llmss_stream_t stream);
+int llmss_ssm_dt(const float* raw, int64_t ldr, const float* dt_bias, const float* a_log, float* dt, float* logdecay, int T, int H,
+                 llmss_stream_t stream);
+/* decay_kind 0: decay[H] values; 1: [T, H] log decays; 2: [T, H * dk] log decays.  state: [slots, H, dv, dk] 32-bit */
+int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv, const float* decay,
+                      int64_t ldd, int decay_kind, const float* bonus, const float* vscale, int64_t ldvs, float* out, float* state,
+                      const int* cu_q, const int* seq_lens, const int* slots, int B, int heads, int qk_heads, int dk, int dv,
+                      int read_before, llmss_stream_t stream);
+int llmss_gated_rmsnorm(const float* o, int64_t ldo, const float* gate, int64_t ldg, int gate_act, const float* weight, int groups,
+                        float eps, int gate_first, const float* skip_x, int64_t ldx, const float* skip_d, int H, void* out, int T,
+                        int C, int dtype, llmss_stream_t stream);
+int llmss_qknorm_kv_write(const float* qkv, int64_t ld, int hq, int hkv, int dk, int dv, const float* q_w, const float* k_w, float eps,
+                          float temp_coef, int temp_every, const int* positions, const int* slots, void* k_cache, void* v_cache,
+                          int block_size, void* q_out, int T, int dtype, llmss_stream_t stream);
+int llmss_attention_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                         int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias, int n_dist,
+                         const float* gate, int64_t ldg, void* out, int B, int max_q, int hq, int hkv, int dk, int dv, float scale,
+                         int dtype, llmss_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -120,6 +120,26 @@ _SIGS = {
     "llmss_moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "llmss_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "llmss_moe_scale": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "llmss_embed_bigram": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "llmss_postnorm_residual": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                        c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p]),
+    "llmss_token_shift": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                  c_int, c_void_p, c_int, c_void_p]),
+    "llmss_causal_conv": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "llmss_unary_f32": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "llmss_ssm_dt": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "llmss_linear_scan": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p,
+                                  c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, c_void_p]),
+    "llmss_gated_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int64,
+                                    c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "llmss_qknorm_kv_write": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "llmss_attention_bias": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                     c_void_p]),
 }
 _OPTIONAL = {
     "llmss_attn_prefill_paged": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,

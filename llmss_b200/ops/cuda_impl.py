@@ -597,3 +597,148 @@ def moe_experts_grouped(h, ids, wts, w_up, w_down, act, gated: bool = False):
                "llmss_moe_combine")
     _count()
     return out
+
+
+# --------------------------------------------------------------------------- recurrent layers, post-norm residual
+def _f32rows(x):
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1, "expected a 32-bit 2-D tensor with contiguous rows"
+    return x.shape[0], x.shape[1], x.stride(0)
+
+
+def _bq(batch):
+    assert batch.state_slots is not None, "the batch names no state slots"
+    return _ptr(batch.cu_q), _ptr(batch.seq_lens), _ptr(batch.state_slots), batch.num_seqs, max(1, batch.max_q)
+
+
+def embed_bigram(tokens, wte, table, mul_prev, mul_cur, buckets, batch, prev_state):
+    lib = _lib.load()
+    T = tokens.numel()
+    V, W = wte.shape
+    assert table.shape[0] > buckets and table.dtype == wte.dtype and wte.is_contiguous() and table.is_contiguous()
+    out = torch.empty(T, W, dtype=torch.float32, device=wte.device)
+    cu, sl, ss, B, mq = _bq(batch)
+    rc = lib.llmss_embed_bigram(_ptr(tokens), _ptr(wte), _ptr(table), _ptr(out), T, W, V, int(mul_prev), int(mul_cur), int(buckets),
+                                cu, sl, ss, B, mq, _ptr(prev_state), _DT[wte.dtype], _stream())
+    _lib.check(rc, "llmss_embed_bigram")
+    _count()
+    return out
+
+
+def postnorm_residual(y, weight, eps, resid=None, y2=None, w_a=None, w_b=None, one_plus=True, out_dtype=None):
+    lib = _lib.load()
+    T, W, ldy = _f32rows(y)
+    dt = out_dtype or torch.float32
+    out = torch.empty(T, W, dtype=dt, device=y.device)
+    new_res = torch.empty(T, W, dtype=torch.float32, device=y.device) if resid is not None else None
+    rc = lib.llmss_postnorm_residual(_ptr(y), ldy, _ptr(y2), y2.stride(0) if y2 is not None else 0, _ptr(w_a), _ptr(w_b), _ptr(weight),
+                                     _ptr(resid), resid.stride(0) if resid is not None else 0, _ptr(new_res), _ptr(out), T, W,
+                                     float(eps), 1 if one_plus else 0, _DT[dt], _stream())
+    _lib.check(rc, "llmss_postnorm_residual")
+    _count()
+    return out, new_res
+
+
+def token_shift(x, mu, batch, prev_state, out_dtype=None):
+    lib = _lib.load()
+    T, W, ldx = _f32rows(x)
+    S = mu.shape[0]
+    dt = out_dtype or torch.float32
+    out = torch.empty(S, T, W, dtype=dt, device=x.device)
+    cu, sl, ss, B, mq = _bq(batch)
+    rc = lib.llmss_token_shift(_ptr(x), ldx, _ptr(mu), S, _ptr(out), T, W, cu, sl, ss, B, mq, _ptr(prev_state), _DT[dt], _stream())
+    _lib.check(rc, "llmss_token_shift")
+    _count()
+    return out
+
+
+def causal_conv(u, w, bias, act, batch, state):
+    lib = _lib.load()
+    T, C, ldu = _f32rows(u)
+    assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C
+    out = torch.empty(T, C, dtype=torch.float32, device=u.device)
+    cu, sl, ss, B, mq = _bq(batch)
+    rc = lib.llmss_causal_conv(_ptr(u), ldu, _ptr(w), _ptr(bias), _ptr(out), T, C, w.shape[1], act, cu, sl, ss, B, mq, _ptr(state),
+                               _stream())
+    _lib.check(rc, "llmss_causal_conv")
+    _count()
+    return out
+
+
+def unary(x, op, out_dtype=None):
+    lib = _lib.load()
+    T, C, ldx = _f32rows(x)
+    dt = out_dtype or torch.float32
+    out = torch.empty(T, C, dtype=dt, device=x.device)
+    _lib.check(lib.llmss_unary_f32(_ptr(x), ldx, _ptr(out), T, C, op, _DT[dt], _stream()), "llmss_unary_f32")
+    _count()
+    return out
+
+
+def ssm_dt(dt_raw, dt_bias, a_log):
+    lib = _lib.load()
+    T, H, ldr = _f32rows(dt_raw)
+    dt = torch.empty(T, H, dtype=torch.float32, device=dt_raw.device)
+    ld = torch.empty(T, H, dtype=torch.float32, device=dt_raw.device)
+    _lib.check(lib.llmss_ssm_dt(_ptr(dt_raw), ldr, _ptr(dt_bias), _ptr(a_log), _ptr(dt), _ptr(ld), T, H, _stream()), "llmss_ssm_dt")
+    _count()
+    return dt, ld
+
+
+def linear_scan(q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, dv, bonus=None, v_scale=None, read_before=False):
+    lib = _lib.load()
+    T, _, ldv = _f32rows(v)
+    _, _, ldq = _f32rows(q)
+    _, _, ldk = _f32rows(k)
+    assert decay.dtype == torch.float32 and state.dtype == torch.float32 and state.is_contiguous()
+    out = torch.empty(T, heads * dv, dtype=torch.float32, device=v.device)
+    cu, sl, ss, B, _ = _bq(batch)
+    rc = lib.llmss_linear_scan(_ptr(q), ldq, _ptr(k), ldk, _ptr(v), ldv, _ptr(decay), decay.stride(0) if decay.dim() == 2 else 0,
+                               decay_kind, _ptr(bonus), _ptr(v_scale), v_scale.stride(0) if v_scale is not None else 0, _ptr(out),
+                               _ptr(state), cu, sl, ss, B, heads, qk_heads, dk, dv, 1 if read_before else 0, _stream())
+    _lib.check(rc, "llmss_linear_scan")
+    _count()
+    return out
+
+
+def gated_rmsnorm(o, gate, gate_act, weight, groups, eps, gate_first, skip_x=None, skip_d=None, out_dtype=None):
+    lib = _lib.load()
+    T, C, ldo = _f32rows(o)
+    dt = out_dtype or torch.float32
+    out = torch.empty(T, C, dtype=dt, device=o.device)
+    rc = lib.llmss_gated_rmsnorm(_ptr(o), ldo, _ptr(gate), gate.stride(0) if gate is not None else 0, gate_act, _ptr(weight), groups,
+                                 float(eps), 1 if gate_first else 0, _ptr(skip_x), skip_x.stride(0) if skip_x is not None else 0,
+                                 _ptr(skip_d), skip_d.numel() if skip_d is not None else 0, _ptr(out), T, C, _DT[dt], _stream())
+    _lib.check(rc, "llmss_gated_rmsnorm")
+    _count()
+    return out
+
+
+def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions, slot_mapping, k_cache, v_cache,
+                    out_dtype=None):
+    lib = _lib.load()
+    T, _, ld = _f32rows(qkv)
+    dt = out_dtype or k_cache.dtype
+    assert k_cache.dtype == dt and v_cache.dtype == dt and k_cache.is_contiguous() and v_cache.is_contiguous()
+    q = torch.empty(T, hq * dk, dtype=dt, device=qkv.device)
+    rc = lib.llmss_qknorm_kv_write(_ptr(qkv), ld, hq, hkv, dk, dv, _ptr(q_w), _ptr(k_w), float(eps), float(temp_coef), int(temp_every),
+                                   _ptr(positions), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), k_cache.shape[2], _ptr(q), T,
+                                   _DT[dt], _stream())
+    _lib.check(rc, "llmss_qknorm_kv_write")
+    _count()
+    return q
+
+
+def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None):
+    lib = _lib.load()
+    T = q.shape[0]
+    dt = q.dtype
+    assert k_cache.dtype == dt and (out_dtype or dt) == dt and q.stride(1) == 1
+    out = torch.empty(T, hq * dv, dtype=dt, device=q.device)
+    rc = lib.llmss_attention_bias(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
+                                  batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
+                                  _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(gate),
+                                  gate.stride(0) if gate is not None else 0, _ptr(out), batch.num_seqs, max(1, batch.max_q), hq, hkv,
+                                  dk, dv, float(scale), _DT[dt], _stream())
+    _lib.check(rc, "llmss_attention_bias")
+    _count()
+    return out

@@ -139,12 +139,141 @@ PRESETS.update({
 })
 
 
+def ninelix_config(width: int, vocab: int, layers, buckets: int = 251, mul_prev: int = 31, mul_cur: int = 7, logit_scale: float = 1.0,
+                   eps: float = 1e-6) -> dict:
+    """config.json of a Ninelix model.  ``layers``: one dict per layer, {"type": "wkv", "heads", "dim", "lora"} |
+    {"type": "lightning", "heads", "dim", "vdim", optionally "decay"} | {"type": "parallel", "left": {heads, kv_heads, dim, vdim, conv,
+    bias_max, buckets, optionally scale, q_temp}, "right": {heads, vdim, state, groups, norm_groups, conv}}, each with
+    "mlp": None | {"kind": "dense", "ff"} | {"kind": "moe", "experts", "top", "ff"}.  ``lora`` (rows of the decay's low-rank
+    projection) and ``buckets`` (rows of the distance table) only size the random tensors: a model reads them off the tensors."""
+    out = []
+    for L in layers:
+        f = L.get("mlp")
+        if f is not None and f["kind"] == "moe":
+            f = {"kind": "moe", "expert": {"ff": f["ff"]}, "router": {"experts": f["experts"], "top": f["top"]}}
+        elif f is not None:
+            f = {"kind": "dense", "ff": f["ff"]}
+        if L["type"] == "wkv":
+            m = {"heads": L["heads"], "dim": L["dim"], "lora": L.get("lora", 16)}
+        elif L["type"] == "lightning":
+            H = L["heads"]
+            m = {"heads": H, "dim": L["dim"], "vdim": L["vdim"],
+                 "decay": L.get("decay") or [1.0 - 2.0 ** -(1.0 + 6.0 * h / max(1, H - 1)) for h in range(H)]}
+        else:
+            a, r = dict(L["left"]), dict(L["right"])
+            a.setdefault("scale", a["dim"] ** -0.5)
+            a.setdefault("q_temp", {"coef": 0.25, "every": 32})
+            a.setdefault("buckets", 16)
+            m = {"left": a, "right": r}
+        out.append({"type": L["type"], "mixer": m, "mlp": f})
+    return {"architecture": "Ninelix", "vocab": vocab, "width": width, "norm": {"eps": eps}, "logit_scale": logit_scale,
+            "embedding": {"bigram": {"buckets": buckets, "mul_prev": mul_prev, "mul_cur": mul_cur}}, "layers": out}
+
+
+def _ninelix_shapes(cfg: dict):
+    W, V = cfg["width"], cfg["vocab"]
+    yield "embed", (V, W), "unit"
+    yield "bigram", (cfg["embedding"]["bigram"]["buckets"] + 1, W), ("n", 0.0, 0.5)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}", L["mixer"]
+        yield f"{p}.norm1", (W,), ("n", 0.0, 0.1)
+        q = f"{p}.mix"
+        if L["type"] == "wkv":
+            n, r = m["heads"] * m["dim"], m.get("lora", 16)
+            for s in "rkvgw":
+                yield f"{q}.mu.{s}", (W,), ("u", 0.0, 1.0)
+            for s in "rkvg":
+                yield f"{q}.{s}", (n, W), "fan"
+            yield f"{q}.w1", (r, W), "fan"
+            yield f"{q}.w2", (n, r), "fan"
+            yield f"{q}.w0", (n,), ("n", -1.0, 1.0)
+            yield f"{q}.u", (m["heads"], m["dim"]), ("n", 0.0, 0.5)
+            yield f"{q}.norm", (n,), "ln_w"
+            yield f"{q}.o", (W, n), "fan"
+        elif L["type"] == "lightning":
+            nk, nv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            yield f"{q}.q", (nk, W), "fan"
+            yield f"{q}.k", (nk, W), "fan"
+            yield f"{q}.v", (nv, W), "fan"
+            yield f"{q}.g", (nv, W), "fan"
+            yield f"{q}.norm", (nv,), "ln_w"
+            yield f"{q}.o", (W, nv), "fan"
+        else:
+            a, r = m["left"], m["right"]
+            for s, n in (("q", a["heads"] * a["dim"]), ("k", a["kv_heads"] * a["dim"]), ("v", a["kv_heads"] * a["vdim"])):
+                yield f"{q}.left.{s}", (n, W), "fan"
+                yield f"{q}.left.{s}.b", (n,), ("n", 0.0, 0.1)
+                yield f"{q}.left.{s}.conv", (n, a["conv"]), ("n", 0.0, a["conv"] ** -0.5)
+            yield f"{q}.left.q.norm", (a["dim"],), "ln_w"
+            yield f"{q}.left.k.norm", (a["dim"],), "ln_w"
+            yield f"{q}.left.rel", (a.get("buckets", 16), a["heads"]), ("n", 0.0, 1.0)
+            yield f"{q}.left.g", (a["heads"], W), "fan"
+            yield f"{q}.left.o", (W, a["heads"] * a["vdim"]), "fan"
+            inner, gn = r["heads"] * r["vdim"], r["groups"] * r["state"]
+            yield f"{q}.right.in", (2 * inner + 2 * gn + r["heads"], W), "fan"
+            yield f"{q}.right.conv", (inner + 2 * gn, r["conv"]), ("n", 0.0, r["conv"] ** -0.5)
+            yield f"{q}.right.conv.b", (inner + 2 * gn,), ("n", 0.0, 0.1)
+            yield f"{q}.right.dt_bias", (r["heads"],), ("n", -1.0, 1.0)
+            yield f"{q}.right.A_log", (r["heads"],), ("n", 0.0, 0.7)
+            yield f"{q}.right.D", (r["heads"],), "ln_w"
+            yield f"{q}.right.norm", (inner,), "ln_w"
+            yield f"{q}.right.o", (W, inner), "fan"
+            yield f"{q}.left.out", (W,), "ln_w"
+            yield f"{q}.right.out", (W,), "ln_w"
+        f = L.get("mlp")
+        if f is None:
+            continue
+        yield f"{p}.norm2", (W,), ("n", 0.0, 0.1)
+        if f["kind"] == "dense":
+            yield f"{p}.mlp.up", (f["ff"], W), "fan"
+            yield f"{p}.mlp.down", (W, f["ff"]), "fan"
+        else:
+            F = f["expert"]["ff"]
+            for e in range(f["router"]["experts"]):
+                yield f"{p}.mlp.e{e}.gate", (F, W), "fan"
+                yield f"{p}.mlp.e{e}.up", (F, W), "fan"
+                yield f"{p}.mlp.e{e}.down", (W, F), "fan"
+            yield f"{p}.mlp.router", (f["router"]["experts"], W), "fan2"
+    yield "final.norm", (W,), ("n", 0.0, 0.1)
+    yield "head", (V, W), "fan"
+
+
+def _ninelix_preset(width, vocab, heads, ff, n_blocks, experts=8, top=2, eff=None):
+    """``n_blocks`` x (parallel + dense, wkv + experts, lightning + dense) at head size 64 / 128."""
+    d = 64
+    H = width // d
+    layers = []
+    for _ in range(n_blocks):
+        layers += [
+            {"type": "parallel", "left": dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, conv=3, bias_max=512, buckets=32),
+             "right": dict(heads=H, vdim=d, state=128, groups=max(1, H // 8), norm_groups=max(1, H // 8), conv=4),
+             "mlp": {"kind": "dense", "ff": ff}},
+            {"type": "wkv", "heads": H, "dim": d, "lora": 64, "mlp": {"kind": "moe", "experts": experts, "top": top, "ff": eff or ff // top}},
+            {"type": "lightning", "heads": H // 2, "dim": 128, "vdim": 128, "mlp": {"kind": "dense", "ff": ff}},
+        ]
+    return ninelix_config(width, vocab, layers, buckets=65521, mul_prev=1000003, mul_cur=31)
+
+
+PRESETS.update({
+    "ninelix-tiny": ninelix_config(128, 320, [
+        {"type": "parallel", "left": dict(heads=4, kv_heads=2, dim=24, vdim=16, conv=3, bias_max=40, buckets=12),
+         "right": dict(heads=4, vdim=16, state=24, groups=2, norm_groups=2, conv=4), "mlp": {"kind": "dense", "ff": 192}},
+        {"type": "wkv", "heads": 4, "dim": 24, "lora": 8, "mlp": {"kind": "moe", "experts": 6, "top": 2, "ff": 48}},
+        {"type": "lightning", "heads": 2, "dim": 32, "vdim": 40, "mlp": {"kind": "dense", "ff": 192}}]),
+    # sizes whose layers resemble a served model's (random weights), beside gptj-like-* of equal width and depth
+    "ninelix-2k": _ninelix_preset(2048, 32000, 16, 4096, 6),
+    "ninelix-4k": _ninelix_preset(4096, 32000, 32, 6144, 6),
+})
+
+
 def _shapes(cfg: dict) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
     """(name, shape, kind) for every tensor of the family; kind in {w, b, ln_w, ln_b, emb} (and, for architectures whose
     activations must keep unit scale without trained weights: unit, fan, fan2, alpha, ls)."""
     mt = cfg.get("model_type") or str(cfg["architecture"]).lower()
     if mt == "bedovik":
         yield from _bedovik_shapes(cfg)
+    elif mt == "ninelix":
+        yield from _ninelix_shapes(cfg)
     elif mt == "gptj":
         H, L, V = cfg["n_embd"], cfg["n_layer"], cfg["vocab_size"]
         F = cfg.get("n_inner") or 4 * H
@@ -286,7 +415,10 @@ def write_random_checkpoint(path, preset_or_cfg, dtype=torch.float16, device=Non
             shard, size = {}, 0
 
     for name, shape, kind in _shapes(cfg):
-        if kind in ("unit", "fan", "fan2", "alpha", "ls"):
+        if isinstance(kind, tuple):      # ("n", mean, std): normal; ("u", lo, hi): uniform
+            r = (torch.randn if kind[0] == "n" else torch.rand)(shape, generator=gen, device=device, dtype=torch.float32)
+            t = kind[1] + kind[2] * r if kind[0] == "n" else kind[1] + (kind[2] - kind[1]) * r
+        elif kind in ("unit", "fan", "fan2", "alpha", "ls"):
             r = torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
             t = {"unit": r, "fan": r * shape[-1] ** -0.5 if shape else r, "fan2": 2.0 * r * shape[-1] ** -0.5 if shape else r,
                  "alpha": 0.7 + 0.1 * r, "ls": 0.4 + 0.1 * r}[kind]
