@@ -210,3 +210,17 @@ def forward(tokens, W, cfg, taps=None):
         if taps is not None:
             taps.append(x.clone())
     return (layer_norm(x, W["final.norm"], eps) @ W["head"].T) * cfg["logit_scale"]
+
+
+def load_weights(path):
+    """All tensors of a checkpoint folder as float64."""
+    from pathlib import Path
+
+    from safetensors import safe_open
+
+    out = {}
+    for f in sorted(Path(path).glob("*.safetensors")):
+        with safe_open(str(f), framework="pytorch") as h:
+            for k in h.keys():
+                out[k] = h.get_tensor(k).to(F64)
+    return out

@@ -1,0 +1,141 @@
+"""Ninelix on CUDA: the recurrence scan, token shift, short convolution, grouped gated norm, post-norm residual, biased
+attention and gated experts kernels against the plain float64 oracle.
+
+float32 runs everything in true 32-bit (tight tolerance); bfloat16 is what serving uses (tolerance of 16-bit rounding).
+"""
+import pytest
+import torch
+
+import ninelix_oracle as oracle
+import test_ninelix_cpu as cases
+from llmss_b200 import ops
+from llmss_b200.utils.checkpoint import ninelix_config
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+MODES = [pytest.param(F32, 3e-4, id="f32"), pytest.param(BF16, 8e-2, id="bf16")]
+
+# sizes the kernels tile differently: key sizes over several 16-row strips, value sizes over a warp, many heads per group,
+# more value channels than one block holds, widths that fit the tensor-core GEMM's 16-byte rules
+cases.CONFIGS["wide"] = ninelix_config(128, 211, [
+    {"type": "wkv", "heads": 2, "dim": 64, "lora": 16, "mlp": {"kind": "moe", "experts": 8, "top": 2, "ff": 32}},
+    {"type": "parallel", "left": cases.attn(heads=12, kv_heads=1, dim=40, vdim=72, conv=4, bias_max=100, buckets=14),
+     "right": cases.ssd(heads=4, vdim=32, state=40, groups=2, norm_groups=4, conv=4), "mlp": {"kind": "dense", "ff": 256}},
+    {"type": "lightning", "heads": 2, "dim": 136, "vdim": 24, "mlp": None},
+    {"type": "lightning", "heads": 1, "dim": 48, "vdim": 136, "mlp": None},
+    {"type": "parallel", "left": cases.attn(heads=4, kv_heads=2, dim=128, vdim=64, conv=3, bias_max=70, buckets=8),
+     "right": cases.ssd(heads=2, vdim=64, state=128, groups=1, norm_groups=1, conv=4), "mlp": None}], buckets=101)
+
+
+def test_loaded_library_is_the_in_tree_one():
+    from llmss_b200.ops import _lib
+
+    _lib.load()
+    assert _lib.LOADED_FROM.endswith("llmss_b200/_C/libllmss_b200.so")
+
+
+def test_mechanisms():
+    for taps in (1, 2, 3, 4, 6, 8):
+        cases.test_causal_conv_op(taps, "cuda")
+    for E, top in [(8, 2), (5, 1), (3, 3), (64, 6)]:
+        cases.test_router_is_softmax_over_the_chosen_logits(E, top, "cuda")
+    cases.test_gated_experts_op("cuda", F32, 1e-5)
+    cases.test_gated_experts_op("cuda", BF16, 3e-2)
+
+
+@pytest.mark.parametrize("kind,dk,dv,heads,qk_heads,read_before", [(0, 16, 16, 2, 2, False), (0, 136, 24, 2, 2, False), (1, 40, 32, 4, 2, False),
+                                                                   (1, 128, 64, 2, 1, False), (2, 48, 48, 3, 3, True), (2, 64, 64, 2, 2, True),
+                                                                   (2, 20, 136, 1, 1, True), (1, 300, 8, 2, 2, False)])
+def test_linear_scan_kernel_against_the_plain_recurrence(kind, dk, dv, heads, qk_heads, read_before):
+    """Portions of 1, 2 and more rows of two sequences, states carried in slots that held other values before."""
+    torch.manual_seed(dk + dv)
+    n = [37, 21]
+    rep = heads // qk_heads
+    mk = lambda T, c: torch.randn(T, c, dtype=torch.float64) * 0.5
+    data = []
+    for T in n:
+        q, k, v = mk(T, qk_heads * dk), mk(T, qk_heads * dk), mk(T, heads * dv)
+        dec = {0: torch.rand(heads, dtype=torch.float64), 1: -torch.rand(T, heads, dtype=torch.float64),
+               2: -torch.rand(T, heads * dk, dtype=torch.float64)}[kind]
+        c = torch.rand(T, heads, dtype=torch.float64) + 0.5
+        data.append((q, k, v, dec, c))
+    u = torch.randn(heads, dk, dtype=torch.float64) * 0.3
+    want = []
+    for (q, k, v, dec, c), T in zip(data, n):
+        out = torch.zeros(T, heads, dv, dtype=torch.float64)
+        for h in range(heads):
+            S = torch.zeros(dk, dv, dtype=torch.float64)
+            g = h // rep
+            for t in range(T):
+                a = dec[h] if kind == 0 else torch.exp(dec[t, h]) if kind == 1 else torch.exp(dec[t, h * dk:(h + 1) * dk])[:, None]
+                kv = torch.outer(k[t, g * dk:(g + 1) * dk], c[t, h] * v[t, h * dv:(h + 1) * dv])
+                if read_before:
+                    out[t, h] = (S + u[h][:, None] * kv).T @ q[t, g * dk:(g + 1) * dk]
+                    S = a * S + kv
+                else:
+                    S = a * S + kv
+                    out[t, h] = S.T @ q[t, g * dk:(g + 1) * dk]
+        want.append(out.reshape(T, heads * dv))
+    state = torch.full((3, heads, dk, dv), 3.0, device="cuda")
+    got, at = [[], []], [0, 0]
+    f = lambda x: x.float().cuda()
+    for sizes in ([1, 4], [2, 1], [1, 1], [17, 2], [16, 13], [40, 0]):
+        live = [i for i in (0, 1) if sizes[i] > 0 and at[i] < n[i]]
+        lens = [min(sizes[i], n[i] - at[i]) for i in live]
+        batch = cases.fake_batch(lens, [at[i] for i in live], [2 - i for i in live], "cuda", bs=64)
+        cat = lambda j: torch.cat([data[i][j][at[i]:at[i] + m] for i, m in zip(live, lens)])
+        dec = f(data[0][3]) if kind == 0 else f(cat(3))
+        o = ops.linear_scan(f(cat(0)), f(cat(1)), f(cat(2)), dec, kind, batch, state, heads, qk_heads, dk, dv,
+                            bonus=f(u) if read_before else None, v_scale=f(cat(4)), read_before=read_before).cpu()
+        p = 0
+        for i, m in zip(live, lens):
+            got[i].append(o[p:p + m])
+            at[i] += m
+            p += m
+    for i in (0, 1):
+        cases.close(torch.cat(got[i]), want[i], 2e-4)
+
+
+@pytest.mark.parametrize("dtype,tol", MODES)
+@pytest.mark.parametrize("name", ["wkv", "lightning", "parallel", "dense", "moe", "mixed", "edges", "wide"])
+def test_model_whole_prompt(tmp_path, dtype, tol, name):
+    cases.test_whole_prompt_and_residual_stream(tmp_path, name, "cuda", dtype, tol)
+
+
+@pytest.mark.parametrize("dtype,tol", MODES)
+def test_model_schedules(tmp_path, dtype, tol):
+    for name in ("mixed", "edges", "wide"):
+        cases.test_decode_token_by_token_and_portions(tmp_path / name, name, "cuda", dtype, tol)
+    cases.test_unequal_batches_against_each_alone(tmp_path / "b", "cuda", dtype, tol)
+    cases.test_first_tokens(tmp_path / "c", "cuda", dtype, tol)
+    cases.test_long_decoding(tmp_path / "d", "cuda", dtype, tol)
+
+
+@pytest.mark.parametrize("dtype,tol", MODES)
+def test_model_pages_slots_far_keys(tmp_path, dtype, tol):
+    cases.test_pages_and_slots_are_used_again(tmp_path / "a", "cuda", dtype, tol)
+    cases.test_far_keys_bucket_edges_and_page_borders(tmp_path / "b", "cuda", dtype, tol if dtype == F32 else 0.15)
+    cases.test_model_call_with_a_past(tmp_path / "c", "cuda", dtype, tol)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("graph", [False, True])
+def test_generation(tmp_path, dtype, graph):
+    """Engine.generate with and without CUDA-graph decode steps (padded batch rows are inert: slot -1)."""
+    cases.test_greedy_generation_through_engine_and_cli(tmp_path, "cuda", dtype, graph)
+
+
+def test_cuda_equals_cpu_engine_on_a_replayed_schedule(tmp_path):
+    """The same mixed schedule through the CPU ops and through the kernels, true 32-bit."""
+    cfg, W, cpu = cases.build(tmp_path / "a", "wide", "cpu", F32)
+    _, _, gpu = cases.build(tmp_path / "b", "wide", "cuda", F32)
+    reqs = {k: cases.tokens_for(cfg, n, 90 + n) for k, n in (("a", 130), ("b", 70), ("c", 3))}
+    plan = [[("a", 65), ("c", 1)], [("a", 1), ("b", 64), ("c", 2)], [("a", 63), ("b", 1)], [("a", 1), ("b", 5)]]
+    at = {k: 0 for k in reqs}
+    for step in plan:
+        entries = []
+        for k, n in step:
+            entries.append((k, reqs[k][at[k]:at[k] + n], list(range(n))))
+            at[k] += n
+        cases.close(gpu.feed(entries), cpu.feed(entries), 3e-4)
