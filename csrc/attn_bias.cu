@@ -49,6 +49,17 @@ __global__ void __launch_bounds__(256) qknorm_kv_write_kernel(const float* __res
   }
 }
 
+// x[t, h * dv + c] *= sigmoid(gate[t, h]) in place: the output gate behind an attention kernel that has no gate of its own
+template <typename T>
+__global__ void __launch_bounds__(256) head_gate_kernel(T* __restrict__ x, int64_t ldx, const float* __restrict__ gate, int64_t ldg,
+                                                        int hq, int dv) {
+  const int64_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < hq * dv; c += 256) {
+    const float g = 1.f / (1.f + expf(-gate[t * ldg + c / dv]));
+    x[t * ldx + c] = from_f32<T>(to_f32(x[t * ldx + c]) * g);
+  }
+}
+
 struct AbArgs {
   const void* q; int64_t ldq;
   const void* k_cache; const void* v_cache;
@@ -160,6 +171,14 @@ LLMSS_API int llmss_qknorm_kv_write(const float* qkv, int64_t ld, int hq, int hk
   LLMSS_BY_DTYPE(dtype, (qknorm_kv_write_kernel<T><<<(unsigned)((units + NW - 1) / NW), NW * 32, 0, stream>>>(
                             qkv, ld, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions, slots, (T*)k_cache, (T*)v_cache,
                             block_size, (T*)q_out, T_)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+LLMSS_API int llmss_head_gate(void* x, int64_t ldx, const float* gate, int64_t ldg, int T_, int hq, int dv, int dtype,
+                              cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  LLMSS_BY_DTYPE(dtype, (head_gate_kernel<T><<<T_, 256, 0, stream>>>((T*)x, ldx, gate, ldg, hq, dv)));
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -58,6 +58,8 @@ struct DArgs {
   int balanced;   // 1: flat partition of all key tiles over the grid (ignores num_splits)
   int max_parts;  // balanced: partial slots per (sequence, q head)
   float scale_log2;
+  const float* bias;   // optional additive score bias [hq][n_dist] in raw-score units (bias / scale), indexed by the
+  int n_dist;          // distance of the key from the query (= the sequence's last token); last column = all larger ones
   int dtype;
 };
 
@@ -536,6 +538,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           for (int i = 0; i < CW; ++i)
             if (kbase + i >= I.t_end) sc[i] = -INFINITY;
         }
+        if (a.bias != nullptr && live) {
+          const float* bt = a.bias + (int64_t)head * a.n_dist;
+          const int dmax = a.n_dist - 1, d0 = a.seq_lens[I.b] - 1 - kbase;
+#pragma unroll
+          for (int i = 0; i < CW; ++i) sc[i] += bt[min(max(d0 - i, 0), dmax)];
+        }
         float m_tile = -INFINITY;
 #pragma unroll
         for (int i = 0; i < CW; ++i) m_tile = fmaxf(m_tile, sc[i]);
@@ -793,10 +801,10 @@ LLMSS_API int llmss_attn_decode_tc_supported(int hq, int hkv, int d, int block_s
 // Tensor-core (tcgen05) paged decode attention: the q heads of a KV group are MMA rows.  Same contract
 // as llmss_attn_decode; `scratch` holds the split-KV partials.  Requires block_size in {16, 32, 64}, head_dim in
 // {64, 128, 256}, hq / hkv <= 128.
-LLMSS_API int llmss_attn_decode_tc(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
-                                   const int* block_tables, int max_blocks, const int* seq_lens, void* out,
-                                   int64_t ldo, float* scratch, int B, int hq, int hkv, int d, int block_size,
-                                   int num_blocks, float scale, int num_splits, int dtype, cudaStream_t stream) {
+static int decode_tc_impl(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                          int max_blocks, const int* seq_lens, void* out, int64_t ldo, float* scratch, int B, int hq, int hkv, int d,
+                          int block_size, int num_blocks, float scale, int num_splits, int dtype, const float* bias, int n_dist,
+                          cudaStream_t stream) {
   LLMSS_REQUIRE(dtype == LLMSS_F16 || dtype == LLMSS_BF16, "attn_decode_tc: dtype must be f16/bf16");
   LLMSS_REQUIRE(d == 64 || d == 128 || d == 256, "attn_decode_tc: head_dim=%d unsupported", d);
   LLMSS_REQUIRE(hq > 0 && hkv > 0, "attn_decode_tc: head counts must be positive (hq=%d hkv=%d)", hq, hkv);
@@ -874,6 +882,8 @@ LLMSS_API int llmss_attn_decode_tc(const void* q, int64_t ldq, const void* k_cac
   a.stages = stages;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.dtype = dtype;
+  a.bias = bias;
+  a.n_dist = n_dist;
   int rc = 0;
 #define LLMSS_DT(T_, D_)                                                         \
   do {                                                                           \
@@ -908,4 +918,22 @@ LLMSS_API int llmss_attn_decode_tc(const void* q, int64_t ldq, const void* k_cac
     return 0;
   }
   return llmss_attn_decode_combine(a.part_o, a.part_ml, out, ldo, B, hq, d, num_splits, dtype, stream);
+}
+
+LLMSS_API int llmss_attn_decode_tc(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                   const int* block_tables, int max_blocks, const int* seq_lens, void* out,
+                                   int64_t ldo, float* scratch, int B, int hq, int hkv, int d, int block_size,
+                                   int num_blocks, float scale, int num_splits, int dtype, cudaStream_t stream) {
+  return decode_tc_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, scratch, B, hq, hkv, d, block_size,
+                        num_blocks, scale, num_splits, dtype, nullptr, 0, stream);
+}
+
+// The same with an additive score bias per head and distance (bias_over_scale [hq][n_dist] = bias / scale, scale > 0).
+LLMSS_API int llmss_attn_decode_tc_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                        const int* block_tables, int max_blocks, const int* seq_lens, void* out, int64_t ldo,
+                                        float* scratch, int B, int hq, int hkv, int d, int block_size, int num_blocks, float scale,
+                                        int num_splits, int dtype, const float* bias_over_scale, int n_dist, cudaStream_t stream) {
+  LLMSS_REQUIRE(bias_over_scale != nullptr && n_dist > 0 && scale > 0.f, "attn_decode_tc_bias: needs a bias table and a positive scale");
+  return decode_tc_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, scratch, B, hq, hkv, d, block_size,
+                        num_blocks, scale, num_splits, dtype, bias_over_scale, n_dist, stream);
 }

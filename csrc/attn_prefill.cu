@@ -78,6 +78,13 @@ struct PArgs {
   int q_col, k_col, v_col;  // first column of q / k / v inside the packed row (elements)
   float scale_log2;
   int dtype;
+  // BIAS instantiation only: an additive score bias per head and distance (pre-divided by the score scale, so that it
+  // joins the raw scores before the one multiply), the last column standing for every larger distance; and an output
+  // gate, sigmoid(gate[token, head]), applied with the final normalisation
+  const float* bias;
+  int n_dist;
+  const float* gate;
+  int64_t ldg;
 };
 
 // MN-major (N contiguous) 128B-swizzled operand: rows are K (keys), 64 elements of N per 128-byte row;
@@ -170,7 +177,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 //                assembled page by page from the paged cache (tmap_k / tmap_v, one TMA box per page and 64-column
 //                chunk, addressed through the block table), which already holds this step's keys (rope_kv_write
 //                runs first).  Query i of a sequence sits at position ctx + i, ctx = seq_len - q_len.
-template <typename T, int D, bool PAGED>
+template <typename T, int D, bool PAGED, bool BIAS = false>
 __global__ void __launch_bounds__(kThreads, PCfg<D>::MIN_CTAS)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ PArgs a) {
@@ -398,6 +405,18 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_sfree[j & 1]);  // S_j is in registers: the buffer can take QK_{j+2}
+      if constexpr (BIAS) {
+        const float* bt = a.bias + (int64_t)head * a.n_dist;
+        const int dmax = a.n_dist - 1, d0 = qpos - kbase;   // distance from this row to the tile's first key
+        if (d0 - (BN - 1) >= dmax) {                        // the whole tile lies at or beyond the table's last column
+          const float cb = bt[dmax];
+#pragma unroll
+          for (int i = 0; i < BN; ++i) sc[i] += cb;
+        } else {
+#pragma unroll
+          for (int i = 0; i < BN; ++i) sc[i] += bt[min(max(d0 - i, 0), dmax)];
+        }
+      }
       if (diag) {
 #pragma unroll
         for (int i = 0; i < BN; ++i)
@@ -483,7 +502,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     // epilogue: O / l -> out
     mbar_wait(&bar_o[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 72);
     tcgen05_fence_after();
-    const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+    float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+    if constexpr (BIAS) {
+      if (a.gate != nullptr && qrow < len) inv_l *= 1.0f / (1.0f + __expf(-a.gate[(int64_t)(seq_start + qrow) * a.ldg + head]));
+    }
     T* orow = reinterpret_cast<T*>(a.out) + (int64_t)(seq_start + qrow) * a.ldo + (int64_t)head * D;
 #pragma unroll 1
     for (int c = 0; c < D / 32; ++c) {
@@ -525,12 +547,12 @@ PFN_encodeTiled get_encode() {
   return fn;
 }
 
-template <typename T, int D, bool PAGED>
+template <typename T, int D, bool PAGED, bool BIAS = false>
 int launch_prefill(const CUtensorMap& tm, const CUtensorMap& tk, const CUtensorMap& tv, const PArgs& a, int num_seqs,
                    int max_seqlen, cudaStream_t stream) {
   using C = PCfg<D>;
   static PerDeviceSmem configured;
-  auto kern = attn_prefill_kernel<T, D, PAGED>;
+  auto kern = attn_prefill_kernel<T, D, PAGED, BIAS>;
   LLMSS_CHECK_CUDA(configured.ensure(kern, C::SMEM_BYTES));
   dim3 grid((max_seqlen + BM - 1) / BM, a.hq, num_seqs);
   LLMSS_CHECK_CUDA(launch_pdl(kern, grid, dim3(kThreads), (size_t)C::SMEM_BYTES, stream, tm, tk, tv, a));
@@ -619,10 +641,10 @@ LLMSS_API int llmss_attn_prefill(const void* q, int64_t ldq, const void* k, int6
 // q: [total_q, >= hq * d] query rows of the packed activation (row stride ldq); K / V: the paged caches
 // [num_blocks, hkv, block_size, d] which already contain this step's keys and values; seq_lens[i] = cached length of
 // sequence i INCLUDING its cu_q[i+1] - cu_q[i] new tokens; out may alias q.  block_size in {16, 32, 64}.
-LLMSS_API int llmss_attn_prefill_paged(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
-                                       const int* block_tables, int max_blocks, const int* seq_lens, void* out, int64_t ldo,
-                                       const int* cu_q, int num_seqs, int max_q, int total_q, int hq, int hkv, int d,
-                                       int block_size, int num_blocks, float scale, int dtype, cudaStream_t stream) {
+static int prefill_paged_impl(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                              int max_blocks, const int* seq_lens, void* out, int64_t ldo, const int* cu_q, int num_seqs, int max_q,
+                              int total_q, int hq, int hkv, int d, int block_size, int num_blocks, float scale, int dtype,
+                              const float* bias, int n_dist, const float* gate, int64_t ldg, cudaStream_t stream) {
   LLMSS_REQUIRE(dtype == LLMSS_F16 || dtype == LLMSS_BF16, "attn_prefill_paged: dtype must be f16/bf16");
   LLMSS_REQUIRE(d == 64 || d == 128 || d == 256, "attn_prefill_paged: head_dim=%d unsupported (64/128/256)", d);
   LLMSS_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attn_prefill_paged: bad head grouping hq=%d hkv=%d", hq, hkv);
@@ -651,7 +673,13 @@ LLMSS_API int llmss_attn_prefill_paged(const void* q, int64_t ldq, const void* k
   a.q_col = 0;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.dtype = dtype;
-#define LLMSS_PP(T_, D_) return launch_prefill<T_, D_, true>(tm, tk, tv, a, num_seqs, max_q, stream)
+  a.bias = bias;
+  a.n_dist = n_dist;
+  a.gate = gate;
+  a.ldg = ldg;
+#define LLMSS_PP(T_, D_)                                                                                  \
+  return bias != nullptr ? launch_prefill<T_, D_, true, true>(tm, tk, tv, a, num_seqs, max_q, stream)     \
+                         : launch_prefill<T_, D_, true, false>(tm, tk, tv, a, num_seqs, max_q, stream)
   if (dtype == LLMSS_F16) {
     if (d == 64) LLMSS_PP(__half, 64);
     if (d == 128) LLMSS_PP(__half, 128);
@@ -662,4 +690,25 @@ LLMSS_API int llmss_attn_prefill_paged(const void* q, int64_t ldq, const void* k
     LLMSS_PP(__nv_bfloat16, 256);
   }
 #undef LLMSS_PP
+}
+
+LLMSS_API int llmss_attn_prefill_paged(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                       const int* block_tables, int max_blocks, const int* seq_lens, void* out, int64_t ldo,
+                                       const int* cu_q, int num_seqs, int max_q, int total_q, int hq, int hkv, int d,
+                                       int block_size, int num_blocks, float scale, int dtype, cudaStream_t stream) {
+  return prefill_paged_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, cu_q, num_seqs, max_q, total_q,
+                            hq, hkv, d, block_size, num_blocks, scale, dtype, nullptr, 0, nullptr, 0, stream);
+}
+
+// The same with a learned distance bias and a per-head output gate (see PArgs): bias_over_scale [hq][n_dist] holds
+// bias / scale (scale > 0), column n_dist - 1 serves every distance from n_dist - 1 on; gate [total_q][>= hq] raw logits
+// (row stride ldg) or null.
+LLMSS_API int llmss_attn_prefill_paged_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                            const int* block_tables, int max_blocks, const int* seq_lens, void* out, int64_t ldo,
+                                            const int* cu_q, int num_seqs, int max_q, int total_q, int hq, int hkv, int d,
+                                            int block_size, int num_blocks, float scale, int dtype, const float* bias_over_scale,
+                                            int n_dist, const float* gate, int64_t ldg, cudaStream_t stream) {
+  LLMSS_REQUIRE(bias_over_scale != nullptr && n_dist > 0 && scale > 0.f, "attn_prefill_paged_bias: needs a bias table and a positive scale");
+  return prefill_paged_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, cu_q, num_seqs, max_q, total_q,
+                            hq, hkv, d, block_size, num_blocks, scale, dtype, bias_over_scale, n_dist, gate, ldg, stream);
 }

@@ -203,6 +203,7 @@ __device__ __forceinline__ float act_t(float x, int runtime_act) {
   else if constexpr (ACT == LLMSS_ACT_GELU_TANH) return 0.5f * x * (1.0f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
   else if constexpr (ACT == LLMSS_ACT_SILU) return __fdividef(x, 1.0f + __expf(-x));
   else if constexpr (ACT == LLMSS_ACT_RELU2) { const float r = fmaxf(x, 0.0f); return r * r; }
+  else if constexpr (ACT == LLMSS_ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
   else return act_fast(x, runtime_act);
 }
 
@@ -254,6 +255,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const float (&v)[
     if (a.act == LLMSS_ACT_GELU_TANH) LLMSS_SC(EPI_ACT, LLMSS_ACT_GELU_TANH);
     else if (a.act == LLMSS_ACT_SILU) LLMSS_SC(EPI_ACT, LLMSS_ACT_SILU);
     else if (a.act == LLMSS_ACT_RELU2) LLMSS_SC(EPI_ACT, LLMSS_ACT_RELU2);
+    else if (a.act == LLMSS_ACT_GELU_ERF) LLMSS_SC(EPI_ACT, LLMSS_ACT_GELU_ERF);
     else LLMSS_SC(EPI_ACT, ACT_RUNTIME);
   } else if (a.epi == EPI_GATED) {
     if (a.act == LLMSS_ACT_SILU) LLMSS_SC(EPI_GATED, LLMSS_ACT_SILU);
@@ -261,6 +263,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const float (&v)[
     else LLMSS_SC(EPI_GATED, ACT_RUNTIME);
   } else {
     if (a.act == LLMSS_ACT_NONE) LLMSS_SC(EPI_F32, LLMSS_ACT_NONE);
+    else if (a.act == LLMSS_ACT_SILU) LLMSS_SC(EPI_F32, LLMSS_ACT_SILU);
     else LLMSS_SC(EPI_F32, ACT_RUNTIME);
   }
 #undef LLMSS_SC
@@ -335,6 +338,7 @@ __device__ __forceinline__ bool store_chunk_full(const GemmArgs& a, const float 
     if (a.act == LLMSS_ACT_GELU_TANH) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_GELU_TANH>(a, v, n, mb0, lane, bval);
     else if (a.act == LLMSS_ACT_SILU) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_SILU>(a, v, n, mb0, lane, bval);
     else if (a.act == LLMSS_ACT_RELU2) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_RELU2>(a, v, n, mb0, lane, bval);
+    else if (a.act == LLMSS_ACT_GELU_ERF) store_chunk_full_t<T, CH, EPI_ACT, LLMSS_ACT_GELU_ERF>(a, v, n, mb0, lane, bval);
     else store_chunk_full_t<T, CH, EPI_ACT, ACT_RUNTIME>(a, v, n, mb0, lane, bval);
   } else if (a.epi == EPI_GATED) {
     if (a.act == LLMSS_ACT_SILU) store_chunk_full_t<T, CH, EPI_GATED, LLMSS_ACT_SILU>(a, v, n, mb0, lane, bval);

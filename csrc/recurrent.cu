@@ -129,9 +129,11 @@ __global__ void __launch_bounds__(128) token_shift_kernel(const float* __restric
 }
 
 // ------------------------------------------------------------------------------------------------ causal_conv
-constexpr int kConvChunk = 64, kMaxTaps = 8;
+constexpr int kConvChunk = 64, kMaxTapsAny = 16;
 
-// grid (B, ceil(C / 128), token chunks); thread = channel; chunk 0 of a sequence reads and replaces the slot's tail
+// grid (B, ceil(C / 128), token chunks); thread = channel; chunk 0 of a sequence reads and replaces the slot's tail.
+// kMaxTaps bounds the register window (instantiated for 4, 8 and 16 taps).
+template <int kMaxTaps>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restrict__ u, int64_t ldu, const float* __restrict__ w,
                                                           const float* __restrict__ bias, float* __restrict__ out, int C, int taps,
                                                           int act, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
@@ -210,9 +212,20 @@ __global__ void __launch_bounds__(256) ssm_dt_kernel(const float* __restrict__ r
 // ------------------------------------------------------------------------------------------------ linear_scan
 // One block per (sequence, head, slice of value channels).  Thread (j, r) keeps rows [r * 16, r * 16 + 16) of column j
 // of the state in registers (thread index = j * R + r, R a power of two, so the R partial dot products of an output meet
-// in one warp shuffle).  Tokens are staged 16 at a time through shared memory: q, k, per-channel decays, scaled values.
-// The state lies in memory column-major per head ([dv][dk]: a thread's 16 rows are contiguous).
-constexpr int KPT = 16, TCH = 16;
+// in one warp shuffle).  Tokens are staged 16 at a time through shared memory -- q, k, per-channel decays (exponentials
+// taken while staging), scaled values -- in 16-float strips 20 floats apart, so that the strips a warp reads together lie
+// in different banks and every read is a 16-byte one; strips beyond dk hold zeros, which leaves the inner loop without
+// bounds checks.  The state lies in memory column-major per head ([dv][dk]: a thread's 16 rows are contiguous).
+//
+// A recurrence is a dependent chain per token, so one block per (sequence, head) leaves a prompt round of a few long
+// sequences bound by latency.  Long portions therefore run in two passes over chunks of `chunk` tokens, every chunk a block:
+//   pass 1 (MODE 1)  every chunk but a sequence's last runs from a ZERO state and leaves its summary in scratch: the state
+//                    it ends with and the product of its decays (per key row); chunk 0 also copies the sequence's old state;
+//   pass 2 (MODE 2)  chunk c rebuilds its true start state from the old state and the summaries of chunks 0 .. c - 1
+//                    (S <- D_c' S + S_c'), runs its tokens and writes the outputs; the last chunk writes the new state.
+// Pass 2 never reads the state tensor and pass 1 never writes it, so the passes need no ordering inside themselves.
+// MODE 0 is the single pass (decode steps, short portions).
+constexpr int KPT = 16, TCH = 16, STRIP = 20, SCAN_THREADS = 256;
 struct ScanArgs {
   const float* q; int64_t ldq;
   const float* k; int64_t ldk;
@@ -224,78 +237,146 @@ struct ScanArgs {
   float* state;                        // [slots, H, dv, dk]
   const int* cu_q; const int* seq_lens; const int* slots;
   int H, rep, dk, dv, dvt, R;
+  // chunked passes: scratch = [B][H][dv][dk] copies of the old states, then [B][nch][H][dv][dk] chunk states, then
+  // [B][nch][H][dk] decay products
+  float* old_copy; float* chunk_state; float* chunk_decay;
+  int chunk, nch, nslices;
 };
 
-template <bool READ_BEFORE, int KIND>
-__global__ void __launch_bounds__(1024) linear_scan_kernel(ScanArgs a) {
-  extern __shared__ float sm[];
+template <bool READ_BEFORE, int KIND, int MODE>
+__global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(ScanArgs a) {
+  extern __shared__ __align__(16) float sm[];
   const Seq s = seq_of(a.cu_q, a.seq_lens, a.slots, blockIdx.x);
   if (s.ql == 0) return;
-  const int h = blockIdx.y, j0 = blockIdx.z * a.dvt;
+  const int h = blockIdx.y;
+  const int slice = MODE == 0 ? blockIdx.z : blockIdx.z % a.nslices, ch = MODE == 0 ? 0 : blockIdx.z / a.nslices;
+  const int j0 = slice * a.dvt;
+  const int t_lo = MODE == 0 ? 0 : ch * a.chunk, t_hi = MODE == 0 ? s.ql : min(s.ql, t_lo + a.chunk);
+  if (t_lo >= s.ql) return;
+  const bool last_chunk = MODE == 0 || t_hi == s.ql;
   const int nj = min(a.dvt, a.dv - j0);
-  const int dk = a.dk, R = a.R;
+  const int dk = a.dk, R = a.R, row = R * STRIP;      // floats per staged token
   const int jl = threadIdx.x / R, r = threadIdx.x % R;
   const bool live = jl < nj;
   const int j = j0 + jl, i0 = r * KPT;
-  float* qs = sm;                       // [TCH][dk]
-  float* ks = qs + TCH * dk;            // [TCH][dk]
-  float* as = ks + TCH * dk;            // [TCH][dk] (kind 2) or [TCH] (kind 1)
-  float* vs = as + (KIND == 2 ? TCH * dk : TCH);   // [TCH][dvt]
-  float S[KPT], u[KPT];
-  float* sp = a.state + (((int64_t)s.slot * a.H + h) * a.dv + (live ? j : 0)) * dk;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float* qs = sm;                       // [TCH][row]
+  float* ks = qs + TCH * row;           // [TCH][row]
+  float* as = ks + TCH * row;           // [TCH][row] (kind 2) or [TCH] (kind 1)
+  float* vs = as + (KIND == 2 ? TCH * row : TCH);   // [TCH][dvt]
+  float S[KPT], u[KPT], dp[KPT];
+  const int64_t col = live ? j : 0;
+  float* sp = a.state + (((int64_t)s.slot * a.H + h) * a.dv + col) * dk;
+  const bool full = (dk & 3) == 0 && i0 + KPT <= dk;      // this thread's 16 rows exist and are 16-byte aligned
+  auto load16 = [&](const float* p, float (&dst)[KPT], bool on) {
+    if (on && full) {
 #pragma unroll
-  for (int ii = 0; ii < KPT; ++ii) {
-    const int i = i0 + ii;
-    S[ii] = (live && s.ctx > 0 && i < dk) ? sp[i] : 0.f;
-    u[ii] = (READ_BEFORE && a.bonus != nullptr && i < dk) ? a.bonus[(int64_t)h * dk + i] : 0.f;
+      for (int ii = 0; ii < KPT; ii += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p + i0 + ii);
+        dst[ii] = t.x; dst[ii + 1] = t.y; dst[ii + 2] = t.z; dst[ii + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int ii = 0; ii < KPT; ++ii) dst[ii] = (on && i0 + ii < dk) ? p[i0 + ii] : 0.f;
+    }
+  };
+  auto store16 = [&](float* p, const float (&src)[KPT]) {
+    if (full) {
+#pragma unroll
+      for (int ii = 0; ii < KPT; ii += 4) *reinterpret_cast<float4*>(p + i0 + ii) = make_float4(src[ii], src[ii + 1], src[ii + 2], src[ii + 3]);
+    } else {
+#pragma unroll
+      for (int ii = 0; ii < KPT; ++ii) if (i0 + ii < dk) p[i0 + ii] = src[ii];
+    }
+  };
+  const int64_t bh = (int64_t)blockIdx.x * a.H + h;
+  if (MODE == 0) {
+    load16(sp, S, live && s.ctx > 0);
+  } else if (MODE == 1) {
+    if (ch == 0 && live) {               // the old state, for pass 2 (which must not read the state tensor)
+      load16(sp, S, s.ctx > 0);
+      store16(a.old_copy + (bh * a.dv + col) * dk, S);
+    }
+    if (last_chunk) return;              // nobody needs the last chunk's summary
+#pragma unroll
+    for (int ii = 0; ii < KPT; ++ii) { S[ii] = 0.f; dp[ii] = 1.f; }
+  } else {
+    load16(a.old_copy + (bh * a.dv + col) * dk, S, live);
+    for (int c = 0; c < ch; ++c) {
+      const int64_t cb = ((int64_t)blockIdx.x * a.nch + c) * a.H + h;
+      float sl[KPT];
+      load16(a.chunk_state + (cb * a.dv + col) * dk, sl, live);
+      load16(a.chunk_decay + cb * dk, dp, true);
+#pragma unroll
+      for (int ii = 0; ii < KPT; ++ii) S[ii] = fmaf(dp[ii], S[ii], sl[ii]);
+    }
   }
+#pragma unroll
+  for (int ii = 0; ii < KPT; ++ii) u[ii] = (READ_BEFORE && MODE != 1 && a.bonus != nullptr && i0 + ii < dk) ? a.bonus[(int64_t)h * dk + i0 + ii] : 0.f;
   const float a_const = KIND == 0 ? a.decay[h] : 0.f;
   const int hq = h / a.rep;
-  for (int c0 = 0; c0 < s.ql; c0 += TCH) {
-    const int nt = min(TCH, s.ql - c0);
+  for (int c0 = t_lo; c0 < t_hi; c0 += TCH) {
+    const int nt = min(TCH, t_hi - c0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * dk; idx += blockDim.x) {
-      const int tt = idx / dk, i = idx % dk;
+    for (int tt = warp; tt < nt; tt += nwarp) {
       const int64_t t = s.q0 + c0 + tt;
-      qs[tt * dk + i] = a.q[t * a.ldq + (int64_t)hq * dk + i];
-      ks[tt * dk + i] = a.k[t * a.ldk + (int64_t)hq * dk + i];
-      if (KIND == 2) as[tt * dk + i] = expf(a.decay[t * a.ldd + (int64_t)h * dk + i]);
-    }
-    if (KIND == 1) for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) as[tt] = expf(a.decay[(int64_t)(s.q0 + c0 + tt) * a.ldd + h]);
-    for (int idx = threadIdx.x; idx < nt * nj; idx += blockDim.x) {
-      const int tt = idx / nj, jj = idx % nj;
-      const int64_t t = s.q0 + c0 + tt;
-      float val = a.v[t * a.ldv + (int64_t)h * a.dv + j0 + jj];
-      if (a.vscale != nullptr) val *= a.vscale[t * a.ldvs + h];
-      vs[tt * a.dvt + jj] = val;
+      for (int i = lane; i < R * KPT; i += 32) {
+        const int p = tt * row + (i >> 4) * STRIP + (i & 15);
+        const bool in = i < dk;
+        if (MODE != 1) qs[p] = in ? a.q[t * a.ldq + (int64_t)hq * dk + i] : 0.f;
+        ks[p] = in ? a.k[t * a.ldk + (int64_t)hq * dk + i] : 0.f;
+        if (KIND == 2) as[p] = in ? expf(a.decay[t * a.ldd + (int64_t)h * dk + i]) : 0.f;
+      }
+      const float sc = a.vscale != nullptr ? a.vscale[t * a.ldvs + h] : 1.f;
+      for (int jj = lane; jj < nj; jj += 32) vs[tt * a.dvt + jj] = a.v[t * a.ldv + (int64_t)h * a.dv + j0 + jj] * sc;
+      if (KIND == 1 && lane == 0) as[tt] = expf(a.decay[t * a.ldd + h]);
     }
     __syncthreads();
+#pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {
       const float vj = live ? vs[tt * a.dvt + jl] : 0.f;
       const float at = KIND == 1 ? as[tt] : a_const;
-      float acc = 0.f;
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * row + r * STRIP);
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * row + r * STRIP);
+      const float4* a4 = reinterpret_cast<const float4*>(as + tt * row + r * STRIP);
+      float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-      for (int ii = 0; ii < KPT; ++ii) {
-        const int i = i0 + ii;
-        if (i < dk) {
-          const float kv = ks[tt * dk + i] * vj;
-          const float dec = KIND == 2 ? as[tt * dk + i] : at;
-          if (READ_BEFORE) {
-            acc = fmaf(qs[tt * dk + i], fmaf(u[ii], kv, S[ii]), acc);
-            S[ii] = fmaf(dec, S[ii], kv);
+      for (int g = 0; g < KPT / 4; ++g) {
+        const float4 kv4 = k4[g];
+        float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), dv4 = make_float4(at, at, at, at);
+        if (MODE != 1) qv = q4[g];
+        if (KIND == 2) dv4 = a4[g];
+        const float qq[4] = {qv.x, qv.y, qv.z, qv.w}, kk[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int ii = g * 4 + e;
+          const float kv = kk[e] * vj;
+          float& acc = (e & 1) ? acc1 : acc0;
+          if (MODE == 1) {
+            S[ii] = fmaf(dd[e], S[ii], kv);
+            dp[ii] *= dd[e];
+          } else if (READ_BEFORE) {
+            acc = fmaf(qq[e], fmaf(u[ii], kv, S[ii]), acc);
+            S[ii] = fmaf(dd[e], S[ii], kv);
           } else {
-            S[ii] = fmaf(dec, S[ii], kv);
-            acc = fmaf(qs[tt * dk + i], S[ii], acc);
+            S[ii] = fmaf(dd[e], S[ii], kv);
+            acc = fmaf(qq[e], S[ii], acc);
           }
         }
       }
-      for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && r == 0) a.out[(int64_t)(s.q0 + c0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = acc;
+      if (MODE != 1) {
+        float acc = acc0 + acc1;
+        for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (live && r == 0) a.out[(int64_t)(s.q0 + c0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = acc;
+      }
     }
   }
-  if (live) {
-#pragma unroll
-    for (int ii = 0; ii < KPT; ++ii) if (i0 + ii < dk) sp[i0 + ii] = S[ii];
+  if (MODE == 1) {
+    const int64_t cb = ((int64_t)blockIdx.x * a.nch + ch) * a.H + h;
+    if (live) store16(a.chunk_state + (cb * a.dv + col) * dk, S);
+    if (slice == 0 && jl == 0) store16(a.chunk_decay + cb * dk, dp);   // rows beyond dk hold zeros: never stored
+  } else if (live && last_chunk) {
+    store16(sp, S);
   }
 }
 
@@ -394,11 +475,13 @@ LLMSS_API int llmss_token_shift(const float* x, int64_t ldx, const float* mu, in
 LLMSS_API int llmss_causal_conv(const float* u, int64_t ldu, const float* w, const float* bias, float* out, int T_, int C, int taps,
                                 int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state,
                                 cudaStream_t stream) {
-  LLMSS_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal_conv: %d taps (1..%d)", taps, kMaxTaps);
+  LLMSS_REQUIRE(taps >= 1 && taps <= kMaxTapsAny, "causal_conv: %d taps (1..%d)", taps, kMaxTapsAny);
   LLMSS_REQUIRE(taps == 1 || state != nullptr, "causal_conv: more than one tap needs a state");
   if (B <= 0 || T_ <= 0) return 0;
   const dim3 grid(B, (C + 127) / 128, max(1, min((max_q + kConvChunk - 1) / kConvChunk, 64)));
-  causal_conv_kernel<<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  if (taps <= 4) causal_conv_kernel<4><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  else if (taps <= 8) causal_conv_kernel<8><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  else causal_conv_kernel<16><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -420,28 +503,52 @@ LLMSS_API int llmss_ssm_dt(const float* raw, int64_t ldr, const float* dt_bias, 
   return 0;
 }
 
+LLMSS_API int64_t llmss_linear_scan_scratch_floats(int B, int heads, int dk, int dv, int max_q, int chunk) {
+  const int nch = chunk > 0 ? (max_q + chunk - 1) / chunk : 0;
+  return (int64_t)B * heads * ((int64_t)dv * dk + (int64_t)nch * ((int64_t)dv * dk + dk));
+}
+
+// chunk > 0 (and scratch of llmss_linear_scan_scratch_floats floats): two passes over chunks of that many tokens (a
+// multiple of 16) -- for prompt rounds whose sequences are long and few; chunk = 0: one pass.
 LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                                 const float* decay, int64_t ldd, int decay_kind, const float* bonus, const float* vscale,
                                 int64_t ldvs, float* out, float* state, const int* cu_q, const int* seq_lens, const int* slots,
-                                int B, int heads, int qk_heads, int dk, int dv, int read_before, cudaStream_t stream) {
+                                int B, int heads, int qk_heads, int dk, int dv, int read_before, float* scratch, int chunk,
+                                int max_q, cudaStream_t stream) {
   LLMSS_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "linear_scan: %d heads over %d q/k heads", heads, qk_heads);
   LLMSS_REQUIRE(dk > 0 && dk <= 32 * KPT, "linear_scan: key size %d (at most %d)", dk, 32 * KPT);
   LLMSS_REQUIRE(decay_kind >= 0 && decay_kind <= 2, "linear_scan: decay kind %d", decay_kind);
+  LLMSS_REQUIRE(chunk == 0 || (chunk % TCH == 0 && scratch != nullptr && max_q > 0), "linear_scan: bad chunking (%d tokens)", chunk);
   if (B <= 0) return 0;
   ScanArgs a;
   a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.decay = decay; a.ldd = ldd; a.bonus = bonus;
   a.vscale = vscale; a.ldvs = ldvs; a.out = out; a.state = state; a.cu_q = cu_q; a.seq_lens = seq_lens; a.slots = slots;
   a.H = heads; a.rep = heads / qk_heads; a.dk = dk; a.dv = dv;
   a.R = pow2_at_least((dk + KPT - 1) / KPT);
-  a.dvt = min(dv, 1024 / a.R);
+  a.dvt = min(dv, SCAN_THREADS / a.R);
+  a.chunk = chunk;
+  a.nch = chunk > 0 ? (max_q + chunk - 1) / chunk : 1;
+  // few blocks (a prompt round of few sequences): narrower value slices until the grid covers the SMs a few times over
+  while ((int64_t)B * heads * a.nch * ((dv + a.dvt - 1) / a.dvt) < 4 * 148 && a.dvt * a.R > 32 && a.dvt > 4) a.dvt = (a.dvt + 1) / 2;
+  a.nslices = (dv + a.dvt - 1) / a.dvt;
+  a.old_copy = scratch;
+  a.chunk_state = scratch != nullptr ? scratch + (int64_t)B * heads * dv * dk : nullptr;
+  a.chunk_decay = scratch != nullptr ? a.chunk_state + (int64_t)B * a.nch * heads * dv * dk : nullptr;
   const int threads = ((a.dvt * a.R + 31) / 32) * 32;
-  const size_t smem = sizeof(float) * ((size_t)TCH * dk * 2 + (decay_kind == 2 ? (size_t)TCH * dk : TCH) + (size_t)TCH * a.dvt);
-  const dim3 grid(B, heads, (dv + a.dvt - 1) / a.dvt);
-#define LLMSS_SCAN(RB, KIND)                                                                   \
+  const int row = a.R * STRIP;
+  const size_t smem = sizeof(float) * ((size_t)TCH * row * 2 + (decay_kind == 2 ? (size_t)TCH * row : TCH) + (size_t)TCH * a.dvt);
+  const dim3 grid(B, heads, a.nslices * (chunk > 0 ? a.nch : 1));
+  LLMSS_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear_scan: grid too large");
+#define LLMSS_SCAN1(RB, KIND, MODE)                                                            \
   do {                                                                                         \
     static PerDeviceSmem g;                                                                    \
-    LLMSS_CHECK_CUDA(g.ensure(linear_scan_kernel<RB, KIND>, (int)smem));                       \
-    linear_scan_kernel<RB, KIND><<<grid, threads, smem, stream>>>(a);                          \
+    LLMSS_CHECK_CUDA(g.ensure(linear_scan_kernel<RB, KIND, MODE>, (int)smem));                 \
+    linear_scan_kernel<RB, KIND, MODE><<<grid, threads, smem, stream>>>(a);                    \
+  } while (0)
+#define LLMSS_SCAN(RB, KIND)                                                                   \
+  do {                                                                                         \
+    if (chunk > 0) { LLMSS_SCAN1(RB, KIND, 1); LLMSS_SCAN1(RB, KIND, 2); }                     \
+    else LLMSS_SCAN1(RB, KIND, 0);                                                             \
   } while (0)
   if (read_before) {
     if (decay_kind == 0) LLMSS_SCAN(true, 0); else if (decay_kind == 1) LLMSS_SCAN(true, 1); else LLMSS_SCAN(true, 2);
@@ -449,6 +556,7 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
     if (decay_kind == 0) LLMSS_SCAN(false, 0); else if (decay_kind == 1) LLMSS_SCAN(false, 1); else LLMSS_SCAN(false, 2);
   }
 #undef LLMSS_SCAN
+#undef LLMSS_SCAN1
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

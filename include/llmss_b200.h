@@ -266,6 +266,13 @@ int llmss_vp_merge_sample(const float* recs_all, int nranks, int ks, int B, int 
 int llmss_sample(const float* logits, int64_t ld, int B, int vocab, const int* greedy, const float* temperature,
                  const int* top_k, const float* top_p, uint32_t* rng_state, int* out_tokens,
                  long long* out_tokens64, llmss_stream_t stream);
+/* the tcgen05 paged flash kernel with a distance bias (bias_over_scale [hq][n_dist] = bias / scale) and a per-head output
+ * gate sigmoid(gate[token][head]); 16-bit, head_dim 64 / 128 / 256 for keys and values alike */
+int llmss_attn_prefill_paged_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                                  int max_blocks, const int* seq_lens, void* out, int64_t ldo, const int* cu_q, int num_seqs,
+                                  int max_q, int total_q, int hq, int hkv, int d, int block_size, int num_blocks, float scale,
+                                  int dtype, const float* bias_over_scale, int n_dist, const float* gate, int64_t ldg,
+                                  llmss_stream_t stream);
 
 /* ---- recurrent token mixers and the post-normed 32-bit residual stream (csrc/recurrent.cu, csrc/attn_bias.cu).
  * Batch convention: sequence b owns rows cu_q[b]..cu_q[b+1], holds seq_lens[b] tokens including them, and keeps its state
@@ -283,11 +290,19 @@ int llmss_causal_conv(const float* u, int64_t ldu, const float* w, const float* 
 int llmss_unary_f32(const float* x, int64_t ldx, void* out, int rows, int cols, int op, int out_dtype, llmss_stream_t stream);
 int llmss_ssm_dt(const float* raw, int64_t ldr, const float* dt_bias, const float* a_log, float* dt, float* logdecay, int T, int H,
                  llmss_stream_t stream);
-/* decay_kind 0: decay[H] values; 1: [T, H] log decays; 2: [T, H * dk] log decays.  state: [slots, H, dv, dk] 32-bit */
+/* decay_kind 0: decay[H] values; 1: [T, H] log decays; 2: [T, H * dk] log decays.  state: [slots, H, dv, dk] 32-bit.
+ * chunk > 0: two passes over chunks of that many tokens (a multiple of 16), with scratch of llmss_linear_scan_scratch_floats */
+int64_t llmss_linear_scan_scratch_floats(int B, int heads, int dk, int dv, int max_q, int chunk);
 int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv, const float* decay,
                       int64_t ldd, int decay_kind, const float* bonus, const float* vscale, int64_t ldvs, float* out, float* state,
                       const int* cu_q, const int* seq_lens, const int* slots, int B, int heads, int qk_heads, int dk, int dv,
-                      int read_before, llmss_stream_t stream);
+                      int read_before, float* scratch, int chunk, int max_q, llmss_stream_t stream);
+/* tcgen05 decode attention with a score bias per head and key distance; x[t, h * dv + c] *= sigmoid(gate[t, h]) */
+int llmss_attn_decode_tc_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                              int max_blocks, const int* seq_lens, void* out, int64_t ldo, float* scratch, int B, int hq, int hkv,
+                              int d, int block_size, int num_blocks, float scale, int num_splits, int dtype,
+                              const float* bias_over_scale, int n_dist, llmss_stream_t stream);
+int llmss_head_gate(void* x, int64_t ldx, const float* gate, int64_t ldg, int T, int hq, int dv, int dtype, llmss_stream_t stream);
 int llmss_gated_rmsnorm(const float* o, int64_t ldo, const float* gate, int64_t ldg, int gate_act, const float* weight, int groups,
                         float eps, int gate_first, const float* skip_x, int64_t ldx, const float* skip_d, int H, void* out, int T,
                         int C, int dtype, llmss_stream_t stream);

@@ -132,7 +132,8 @@ _SIGS = {
     "llmss_ssm_dt": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "llmss_linear_scan": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p,
                                   c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                  c_int, c_int, c_void_p]),
+                                  c_int, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "llmss_linear_scan_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "llmss_gated_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int64,
                                     c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "llmss_qknorm_kv_write": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int,
@@ -142,6 +143,13 @@ _SIGS = {
                                      c_void_p]),
 }
 _OPTIONAL = {
+    "llmss_attn_decode_tc_bias": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
+                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                          c_int, c_void_p]),
+    "llmss_head_gate": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "llmss_attn_prefill_paged_bias": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
+                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                              c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "llmss_attn_prefill_paged": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                          c_void_p]),

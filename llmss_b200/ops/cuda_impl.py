@@ -224,7 +224,8 @@ def use_tc_decode(hq: int, hkv: int, d: int, block_size: int = 16) -> bool:
     return block_size == 64 or g >= _TC_MIN_GROUP
 
 
-def attn_decode(q_view, k_cache, v_cache, block_tables, seq_lens, out_view, hq, hkv, d, scale, num_splits):
+def attn_decode(q_view, k_cache, v_cache, block_tables, seq_lens, out_view, hq, hkv, d, scale, num_splits, bias_over_scale=None):
+    """``bias_over_scale`` [hq, n_dist] (tensor-core kernel only): additive score bias per head and key distance."""
     lib = _lib.load()
     B = q_view.shape[0]
     bs = k_cache.shape[2]
@@ -238,6 +239,15 @@ def attn_decode(q_view, k_cache, v_cache, block_tables, seq_lens, out_view, hq, 
     elif num_splits == 0:
         n = lib.llmss_attn_decode_tc_balanced_scratch_floats(B, hq, d, block_tables.shape[1], bs)
         scratch = arena(q_view.device).attn_scratch(n, q_view.device)
+    assert bias_over_scale is None or tc, "the score bias rides on the tensor-core decode kernel only"
+    if tc and bias_over_scale is not None:
+        rc = lib.llmss_attn_decode_tc_bias(_ptr(q_view), q_view.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                           block_tables.shape[1], _ptr(seq_lens), _ptr(out_view), out_view.stride(0),
+                                           _ptr(scratch), B, hq, hkv, d, bs, k_cache.shape[0], float(scale), num_splits,
+                                           _DT[q_view.dtype], _ptr(bias_over_scale), bias_over_scale.shape[1], _stream())
+        _lib.check(rc, "llmss_attn_decode_tc_bias")
+        _count(1 if num_splits == 1 else 2)
+        return
     if tc:
         rc = lib.llmss_attn_decode_tc(_ptr(q_view), q_view.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
                                       block_tables.shape[1], _ptr(seq_lens), _ptr(out_view), out_view.stride(0),
@@ -684,6 +694,10 @@ def ssm_dt(dt_raw, dt_bias, a_log):
     return dt, ld
 
 
+_SCAN_CHUNK = int(os.environ.get("LLMSS_SCAN_CHUNK", "128"))          # tokens per chunk of the two-pass recurrence
+_SCAN_CHUNK_MIN = int(os.environ.get("LLMSS_SCAN_CHUNK_MIN", "256"))   # portions from this length on run in two passes
+
+
 def linear_scan(q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, dv, bonus=None, v_scale=None, read_before=False):
     lib = _lib.load()
     T, _, ldv = _f32rows(v)
@@ -691,12 +705,18 @@ def linear_scan(q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, d
     _, _, ldk = _f32rows(k)
     assert decay.dtype == torch.float32 and state.dtype == torch.float32 and state.is_contiguous()
     out = torch.empty(T, heads * dv, dtype=torch.float32, device=v.device)
-    cu, sl, ss, B, _ = _bq(batch)
+    cu, sl, ss, B, mq = _bq(batch)
+    # long portions of few sequences: two passes over chunks, every chunk a block (a recurrence is a chain per token)
+    chunk, scratch = 0, None
+    if mq >= _SCAN_CHUNK_MIN and not torch.cuda.is_current_stream_capturing():
+        chunk = _SCAN_CHUNK
+        scratch = torch.empty(lib.llmss_linear_scan_scratch_floats(B, heads, dk, dv, mq, chunk), dtype=torch.float32, device=v.device)
     rc = lib.llmss_linear_scan(_ptr(q), ldq, _ptr(k), ldk, _ptr(v), ldv, _ptr(decay), decay.stride(0) if decay.dim() == 2 else 0,
                                decay_kind, _ptr(bonus), _ptr(v_scale), v_scale.stride(0) if v_scale is not None else 0, _ptr(out),
-                               _ptr(state), cu, sl, ss, B, heads, qk_heads, dk, dv, 1 if read_before else 0, _stream())
+                               _ptr(state), cu, sl, ss, B, heads, qk_heads, dk, dv, 1 if read_before else 0, _ptr(scratch), chunk, mq,
+                               _stream())
     _lib.check(rc, "llmss_linear_scan")
-    _count()
+    _count(2 if chunk else 1)
     return out
 
 
@@ -728,12 +748,54 @@ def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, 
     return q
 
 
+_BIAS_TC = os.environ.get("LLMSS_ATTN_BIAS_TC", "1") == "1"
+_BIAS_OVER_SCALE = {}
+
+
+def _bias_over_scale(dist_bias, scale):
+    """The distance table in the units of the raw scores (the tensor-core kernel adds it before its one multiply)."""
+    key = (dist_bias.data_ptr(), float(scale))
+    t = _BIAS_OVER_SCALE.get(key)
+    if t is None:
+        t = _BIAS_OVER_SCALE[key] = (dist_bias.float() / float(scale)).contiguous()
+    return t
+
+
+def attention_bias_uses_tc(dtype, dk: int, dv: int, block_size: int, scale: float) -> bool:
+    """16-bit pages with equal key and value size 64 / 128 / 256 run on the tcgen05 paged flash kernel (bias and gate
+    instantiation); everything else -- true 32-bit, other or unequal sizes -- on the generic kernel."""
+    return (_BIAS_TC and dtype != torch.float32 and dk == dv and dk in (64, 128, 256) and block_size in (16, 32, 64) and scale > 0
+            and _lib.has("llmss_attn_prefill_paged_bias"))
+
+
 def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None):
     lib = _lib.load()
     T = q.shape[0]
     dt = q.dtype
     assert k_cache.dtype == dt and (out_dtype or dt) == dt and q.stride(1) == 1
     out = torch.empty(T, hq * dv, dtype=dt, device=q.device)
+    if dist_bias is not None and attention_bias_uses_tc(dt, dk, dv, k_cache.shape[2], scale) and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0:
+        bs = k_cache.shape[2]
+        if (batch.is_decode and _lib.has("llmss_attn_decode_tc_bias") and use_tc_decode(hq, hkv, dk, bs)
+                and lib.llmss_attn_decode_tc_supported(hq, hkv, dk, bs)):
+            # one query per sequence: the split-KV decode kernel (the q heads of a group are its MMA rows), then the gate
+            splits = batch.decode_splits or decode_splits(batch.num_seqs, hq, hkv, dk, batch.max_kv, dt, bs)
+            attn_decode(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, out, hq, hkv, dk, scale, splits,
+                        bias_over_scale=_bias_over_scale(dist_bias, scale))
+            if gate is not None:
+                _lib.check(lib.llmss_head_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), T, hq, dv, _DT[dt], _stream()),
+                           "llmss_head_gate")
+                _count()
+            return out
+        rc = lib.llmss_attn_prefill_paged_bias(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
+                                               batch.block_tables.shape[1], _ptr(batch.seq_lens), _ptr(out), out.stride(0),
+                                               _ptr(batch.cu_q), batch.num_seqs, max(1, batch.max_q), T, hq, hkv, dk,
+                                               k_cache.shape[2], k_cache.shape[0], float(scale), _DT[dt],
+                                               _ptr(_bias_over_scale(dist_bias, scale)), dist_bias.shape[1], _ptr(gate),
+                                               gate.stride(0) if gate is not None else 0, _stream())
+        _lib.check(rc, "llmss_attn_prefill_paged_bias")
+        _count()
+        return out
     rc = lib.llmss_attention_bias(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
                                   batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
                                   _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(gate),

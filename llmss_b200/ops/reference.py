@@ -547,7 +547,12 @@ def distance_bias_table(rel, max_distance: int):
     half = B // 2
     cols = []
     for n in range(max_distance + 1):
-        b = n if n < half else min(B - 1, half + int(math.floor(math.log(n / half) / math.log(max_distance / half) * (B - half))))
+        if n < half:
+            b = n
+        elif half == 0 or max_distance <= half:       # no logarithmic range left: everything from half on shares the last row
+            b = B - 1
+        else:
+            b = min(B - 1, half + int(math.floor(math.log(n / half) / math.log(max_distance / half) * (B - half))))
         cols.append(rel[b].float())
     return torch.stack(cols, dim=1).contiguous()
 

@@ -47,16 +47,32 @@ def test_mechanisms():
 @pytest.mark.parametrize("kind,dk,dv,heads,qk_heads,read_before", [(0, 16, 16, 2, 2, False), (0, 136, 24, 2, 2, False), (1, 40, 32, 4, 2, False),
                                                                    (1, 128, 64, 2, 1, False), (2, 48, 48, 3, 3, True), (2, 64, 64, 2, 2, True),
                                                                    (2, 20, 136, 1, 1, True), (1, 300, 8, 2, 2, False)])
-def test_linear_scan_kernel_against_the_plain_recurrence(kind, dk, dv, heads, qk_heads, read_before):
-    """Portions of 1, 2 and more rows of two sequences, states carried in slots that held other values before."""
+@pytest.mark.parametrize("chunked", [False, True])
+def test_linear_scan_kernel_against_the_plain_recurrence(kind, dk, dv, heads, qk_heads, read_before, chunked, device="cuda"):
+    """Portions of 1, 2 and more rows of two sequences, states carried in slots that held other values before.  ``chunked``:
+    portions of 17 tokens and more run in two passes over 16-token chunks (chunk states and decay products in scratch)."""
+    if device == "cuda":
+        from llmss_b200.ops import cuda_impl as cu
+
+        keep = cu._SCAN_CHUNK, cu._SCAN_CHUNK_MIN
+        cu._SCAN_CHUNK, cu._SCAN_CHUNK_MIN = (16, 17) if chunked else (128, 1 << 30)
+        try:
+            _scan_case(kind, dk, dv, heads, qk_heads, read_before, device)
+        finally:
+            cu._SCAN_CHUNK, cu._SCAN_CHUNK_MIN = keep
+    else:
+        _scan_case(kind, dk, dv, heads, qk_heads, read_before, device)
+
+
+def _scan_case(kind, dk, dv, heads, qk_heads, read_before, device):
     torch.manual_seed(dk + dv)
-    n = [37, 21]
+    n = [85, 45]
     rep = heads // qk_heads
     mk = lambda T, c: torch.randn(T, c, dtype=torch.float64) * 0.5
-    data = []
+    data, head_decay = [], torch.rand(heads, dtype=torch.float64)
     for T in n:
         q, k, v = mk(T, qk_heads * dk), mk(T, qk_heads * dk), mk(T, heads * dv)
-        dec = {0: torch.rand(heads, dtype=torch.float64), 1: -torch.rand(T, heads, dtype=torch.float64),
+        dec = {0: head_decay, 1: -torch.rand(T, heads, dtype=torch.float64),
                2: -torch.rand(T, heads * dk, dtype=torch.float64)}[kind]
         c = torch.rand(T, heads, dtype=torch.float64) + 0.5
         data.append((q, k, v, dec, c))
@@ -77,13 +93,15 @@ def test_linear_scan_kernel_against_the_plain_recurrence(kind, dk, dv, heads, qk
                     S = a * S + kv
                     out[t, h] = S.T @ q[t, g * dk:(g + 1) * dk]
         want.append(out.reshape(T, heads * dv))
-    state = torch.full((3, heads, dk, dv), 3.0, device="cuda")
+    state = torch.full((3, heads, dk, dv), 3.0, device=device)
     got, at = [[], []], [0, 0]
-    f = lambda x: x.float().cuda()
-    for sizes in ([1, 4], [2, 1], [1, 1], [17, 2], [16, 13], [40, 0]):
+    f = lambda x: x.float().to(device)
+    for sizes in ([1, 4], [2, 1], [1, 1], [49, 2], [16, 33], [40, 10]):
         live = [i for i in (0, 1) if sizes[i] > 0 and at[i] < n[i]]
+        if not live:
+            continue
         lens = [min(sizes[i], n[i] - at[i]) for i in live]
-        batch = cases.fake_batch(lens, [at[i] for i in live], [2 - i for i in live], "cuda", bs=64)
+        batch = cases.fake_batch(lens, [at[i] for i in live], [2 - i for i in live], device, bs=64)
         cat = lambda j: torch.cat([data[i][j][at[i]:at[i] + m] for i, m in zip(live, lens)])
         dec = f(data[0][3]) if kind == 0 else f(cat(3))
         o = ops.linear_scan(f(cat(0)), f(cat(1)), f(cat(2)), dec, kind, batch, state, heads, qk_heads, dk, dv,
@@ -94,6 +112,7 @@ def test_linear_scan_kernel_against_the_plain_recurrence(kind, dk, dv, heads, qk
             at[i] += m
             p += m
     for i in (0, 1):
+        assert at[i] == n[i]
         cases.close(torch.cat(got[i]), want[i], 2e-4)
 
 
@@ -139,3 +158,66 @@ def test_cuda_equals_cpu_engine_on_a_replayed_schedule(tmp_path):
             entries.append((k, reqs[k][at[k]:at[k] + n], list(range(n))))
             at[k] += n
         cases.close(gpu.feed(entries), cpu.feed(entries), 3e-4)
+
+
+# key = value size 64 / 128 / 256 in 16-bit: the tensor-core flash kernel with the distance table and the gate; its
+# tables end inside and beyond the context
+cases.CONFIGS["tc_sizes"] = ninelix_config(128, 173, [
+    {"type": "parallel", "left": cases.attn(heads=4, kv_heads=2, dim=64, vdim=64, conv=3, bias_max=50, buckets=12),
+     "right": cases.ssd(heads=2, vdim=16, state=16, groups=1, norm_groups=1, conv=2), "mlp": {"kind": "dense", "ff": 128}},
+    {"type": "parallel", "left": cases.attn(heads=2, kv_heads=1, dim=128, vdim=128, conv=2, bias_max=400, buckets=20),
+     "right": cases.ssd(heads=2, vdim=16, state=16, groups=2, norm_groups=2, conv=2), "mlp": None},
+    {"type": "parallel", "left": cases.attn(heads=3, kv_heads=3, dim=256, vdim=256, conv=2, bias_max=9, buckets=6),
+     "right": cases.ssd(heads=2, vdim=16, state=16, groups=2, norm_groups=1, conv=3), "mlp": None}], buckets=37)
+
+
+@pytest.mark.parametrize("d,hq,hkv,n_dist", [(64, 4, 2, 30), (128, 8, 2, 200), (256, 2, 1, 7), (128, 3, 3, 1)])
+def test_biased_attention_kernels_agree_with_the_plain_formula(d, hq, hkv, n_dist):
+    """Both CUDA forms (tensor-core flash kernel, generic kernel) on the same pages: a whole prompt, a portion over context,
+    single tokens; keys at distances inside, on and beyond the table's end and across page borders."""
+    from llmss_b200.engine.batch import BatchInput
+    from llmss_b200.ops import cuda_impl as cu
+
+    torch.manual_seed(d + hq)
+    bs, dev = 64, "cuda"
+    lens, ctxs = [150, 9, 1, 1], [0, 130, 139, 64]
+    nblk = 4
+    tables = [[1 + i * nblk + j for j in range(nblk)] for i in range(len(lens))]
+    batch = BatchInput.build([[0] * n for n in lens], ctxs, tables, bs, dev, max_blocks=nblk)
+    T = sum(lens)
+    q = torch.randn(T, hq * d, device=dev).to(BF16)
+    kc = torch.randn(1 + len(lens) * nblk, hkv, bs, d, device=dev).to(BF16)
+    vc = torch.randn(1 + len(lens) * nblk, hkv, bs, d, device=dev).to(BF16)
+    bias = (2.0 * torch.randn(hq, n_dist, device=dev)).contiguous()
+    gate = torch.randn(T, hq + 3, device=dev)[:, 1:hq + 1]
+    scale = 2.0 * d ** -0.5
+    want = torch.zeros(T, hq, d, dtype=torch.float64)
+    row = 0
+    for i, (n, c) in enumerate(zip(lens, ctxs)):
+        L = c + n
+        k = kc[tables[i]].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :L].double().cpu()
+        v = vc[tables[i]].permute(1, 0, 2, 3).reshape(hkv, -1, d)[:, :L].double().cpu()
+        for r in range(n):
+            p = c + r
+            for h in range(hq):
+                g = h // (hq // hkv)
+                s = (k[g, :p + 1] @ q[row, h * d:(h + 1) * d].double().cpu()) * scale
+                s = s + torch.stack([bias[h, min(p - j, n_dist - 1)].double().cpu() for j in range(p + 1)])
+                want[row, h] = (torch.softmax(s, 0)[:, None] * v[g, :p + 1]).sum(0) / (1.0 + torch.exp(-gate[row, h].double().cpu()))
+            row += 1
+    assert cu.attention_bias_uses_tc(BF16, d, d, bs, scale)
+    got_tc = ops.attention_bias(q, kc, vc, batch, hq, hkv, d, d, scale, bias, gate=gate, out_dtype=BF16)
+    cu._BIAS_TC = False
+    try:
+        got_generic = ops.attention_bias(q, kc, vc, batch, hq, hkv, d, d, scale, bias, gate=gate, out_dtype=BF16)
+    finally:
+        cu._BIAS_TC = True
+    # 16-bit outputs of values several times the spread the error is measured against
+    cases.close(got_generic, want.reshape(T, -1), 6e-2)
+    cases.close(got_tc, want.reshape(T, -1), 6e-2)
+
+
+def test_model_on_the_tensor_core_attention(tmp_path):
+    cases.test_whole_prompt_and_residual_stream(tmp_path / "a", "tc_sizes", "cuda", BF16, 8e-2)
+    cases.test_decode_token_by_token_and_portions(tmp_path / "b", "tc_sizes", "cuda", BF16, 8e-2)
+    cases.test_whole_prompt_and_residual_stream(tmp_path / "c", "tc_sizes", "cuda", F32, 3e-4)
