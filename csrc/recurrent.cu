@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(128) token_shift_kernel(const float* __restric
   const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
   for (int j = blockIdx.y; j < s.ql; j += gridDim.y) {
     const int64_t t = s.q0 + j;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < W; c += gridDim.z * blockDim.x) {
       const float cur = x[t * ldx + c];
       const float prev = j > 0 ? x[(t - 1) * ldx + c] : (s.ctx > 0 ? prev_state[(int64_t)s.slot * W + c] : 0.f);
       const float d = prev - cur;
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(256) ssm_dt_kernel(const float* __restrict__ r
 //                    (S <- D_c' S + S_c'), runs its tokens and writes the outputs; the last chunk writes the new state.
 // Pass 2 never reads the state tensor and pass 1 never writes it, so the passes need no ordering inside themselves.
 // MODE 0 is the single pass (decode steps, short portions).
-constexpr int KPT = 16, TCH = 16, STRIP = 20, SCAN_THREADS = 256;
+constexpr int TCH = 16, SCAN_THREADS = 256;
 struct ScanArgs {
   const float* q; int64_t ldq;
   const float* k; int64_t ldk;
@@ -243,8 +243,24 @@ struct ScanArgs {
   int chunk, nch, nslices;
 };
 
-template <bool READ_BEFORE, int KIND, int MODE>
+__device__ __forceinline__ float4 ld4(const float* p, int i, int n, bool vec) {   // p[i .. i+3], zeros beyond n
+  if (vec && i + 4 <= n) return *reinterpret_cast<const float4*>(p + i);
+  return make_float4(i < n ? p[i] : 0.f, i + 1 < n ? p[i + 1] : 0.f, i + 2 < n ? p[i + 2] : 0.f, i + 3 < n ? p[i + 3] : 0.f);
+}
+__device__ __forceinline__ void st4(float* p, int i, int n, bool vec, float a, float b, float c, float d) {
+  if (vec && i + 4 <= n) { *reinterpret_cast<float4*>(p + i) = make_float4(a, b, c, d); return; }
+  if (i < n) p[i] = a;
+  if (i + 1 < n) p[i + 1] = b;
+  if (i + 2 < n) p[i + 2] = c;
+  if (i + 3 < n) p[i + 3] = d;
+}
+
+// KPT = key rows per thread.  64 where the key size allows: a warp's lanes then differ only in their value column, the
+// staged q / k / decay reads are the same address for the whole warp (shared memory serves them as broadcasts), and every
+// loaded value feeds a multiply-add in each lane -- with 16 rows the kernel was bound by shared-memory wavefronts.
+template <bool READ_BEFORE, int KIND, int MODE, int KPT>
 __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(ScanArgs a) {
+  constexpr int STRIP = KPT + 4;        // floats between staged strips: different banks for the strips of one warp
   extern __shared__ __align__(16) float sm[];
   const Seq s = seq_of(a.cu_q, a.seq_lens, a.slots, blockIdx.x);
   if (s.ql == 0) return;
@@ -263,120 +279,174 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(ScanArgs a) {
   float* qs = sm;                       // [TCH][row]
   float* ks = qs + TCH * row;           // [TCH][row]
   float* as = ks + TCH * row;           // [TCH][row] (kind 2) or [TCH] (kind 1)
-  float* vs = as + (KIND == 2 ? TCH * row : TCH);   // [TCH][dvt]
-  float S[KPT], u[KPT], dp[KPT];
+  float* us = as + (KIND == 2 ? TCH * row : TCH);            // [TCH][row] bonus * k (READ_BEFORE)
+  float* vs = us + (READ_BEFORE ? TCH * row : 0);            // [TCH][dvt]
+  float S[KPT], dp[KIND == 2 && MODE == 1 ? KPT : 1];
+  float dps = 1.f;                      // decay product of a chunk when it is one number per head
   const int64_t col = live ? j : 0;
   float* sp = a.state + (((int64_t)s.slot * a.H + h) * a.dv + col) * dk;
-  const bool full = (dk & 3) == 0 && i0 + KPT <= dk;      // this thread's 16 rows exist and are 16-byte aligned
-  auto load16 = [&](const float* p, float (&dst)[KPT], bool on) {
-    if (on && full) {
-#pragma unroll
-      for (int ii = 0; ii < KPT; ii += 4) {
-        const float4 t = *reinterpret_cast<const float4*>(p + i0 + ii);
-        dst[ii] = t.x; dst[ii + 1] = t.y; dst[ii + 2] = t.z; dst[ii + 3] = t.w;
-      }
-    } else {
-#pragma unroll
-      for (int ii = 0; ii < KPT; ++ii) dst[ii] = (on && i0 + ii < dk) ? p[i0 + ii] : 0.f;
-    }
-  };
-  auto store16 = [&](float* p, const float (&src)[KPT]) {
-    if (full) {
-#pragma unroll
-      for (int ii = 0; ii < KPT; ii += 4) *reinterpret_cast<float4*>(p + i0 + ii) = make_float4(src[ii], src[ii + 1], src[ii + 2], src[ii + 3]);
-    } else {
-#pragma unroll
-      for (int ii = 0; ii < KPT; ++ii) if (i0 + ii < dk) p[i0 + ii] = src[ii];
-    }
-  };
+  const bool vec = (dk & 3) == 0;       // every row of a state column and of a summary is 16-byte aligned
   const int64_t bh = (int64_t)blockIdx.x * a.H + h;
+  auto load_col = [&](const float* p, bool on) {
+#pragma unroll
+    for (int g = 0; g < KPT; g += 4) {
+      const float4 t = on ? ld4(p, i0 + g, dk, vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[g] = t.x; S[g + 1] = t.y; S[g + 2] = t.z; S[g + 3] = t.w;
+    }
+  };
+  auto store_col = [&](float* p) {
+#pragma unroll
+    for (int g = 0; g < KPT; g += 4) st4(p, i0 + g, dk, vec, S[g], S[g + 1], S[g + 2], S[g + 3]);
+  };
   if (MODE == 0) {
-    load16(sp, S, live && s.ctx > 0);
+    load_col(sp, live && s.ctx > 0);
   } else if (MODE == 1) {
     if (ch == 0 && live) {               // the old state, for pass 2 (which must not read the state tensor)
-      load16(sp, S, s.ctx > 0);
-      store16(a.old_copy + (bh * a.dv + col) * dk, S);
+      load_col(sp, s.ctx > 0);
+      store_col(a.old_copy + (bh * a.dv + col) * dk);
     }
     if (last_chunk) return;              // nobody needs the last chunk's summary
 #pragma unroll
-    for (int ii = 0; ii < KPT; ++ii) { S[ii] = 0.f; dp[ii] = 1.f; }
+    for (int ii = 0; ii < KPT; ++ii) S[ii] = 0.f;
+    if (KIND == 2) {
+#pragma unroll
+      for (int ii = 0; ii < (KIND == 2 && MODE == 1 ? KPT : 1); ++ii) dp[ii] = 1.f;
+    }
   } else {
-    load16(a.old_copy + (bh * a.dv + col) * dk, S, live);
+    load_col(a.old_copy + (bh * a.dv + col) * dk, live);
     for (int c = 0; c < ch; ++c) {
       const int64_t cb = ((int64_t)blockIdx.x * a.nch + c) * a.H + h;
-      float sl[KPT];
-      load16(a.chunk_state + (cb * a.dv + col) * dk, sl, live);
-      load16(a.chunk_decay + cb * dk, dp, true);
+      const float* cs = a.chunk_state + (cb * a.dv + col) * dk;
+      const float* cd = a.chunk_decay + cb * dk;
 #pragma unroll
-      for (int ii = 0; ii < KPT; ++ii) S[ii] = fmaf(dp[ii], S[ii], sl[ii]);
+      for (int g = 0; g < KPT; g += 4) {
+        const float4 sl = live ? ld4(cs, i0 + g, dk, vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 d4 = ld4(cd, i0 + g, dk, vec);
+        S[g] = fmaf(d4.x, S[g], sl.x); S[g + 1] = fmaf(d4.y, S[g + 1], sl.y);
+        S[g + 2] = fmaf(d4.z, S[g + 2], sl.z); S[g + 3] = fmaf(d4.w, S[g + 3], sl.w);
+      }
     }
   }
-#pragma unroll
-  for (int ii = 0; ii < KPT; ++ii) u[ii] = (READ_BEFORE && MODE != 1 && a.bonus != nullptr && i0 + ii < dk) ? a.bonus[(int64_t)h * dk + i0 + ii] : 0.f;
   const float a_const = KIND == 0 ? a.decay[h] : 0.f;
   const int hq = h / a.rep;
+  const float* bon = (READ_BEFORE && a.bonus != nullptr) ? a.bonus + (int64_t)h * dk : nullptr;
+  if (MODE == 0 && s.ql == 1) {
+    // a decode step: one token, nothing to share through shared memory -- every thread fetches its rows of q, k and the
+    // decays itself (the threads of a column group read the same lines), so these loads and the state's are in flight together
+    const int64_t t = s.q0;
+    const float* qp = a.q + t * a.ldq + (int64_t)hq * dk;
+    const float* kp = a.k + t * a.ldk + (int64_t)hq * dk;
+    const float* dpp = KIND == 2 ? a.decay + t * a.ldd + (int64_t)h * dk : nullptr;
+    const bool vq = vec && ((reinterpret_cast<uintptr_t>(qp) | reinterpret_cast<uintptr_t>(kp) | reinterpret_cast<uintptr_t>(dpp) |
+                             reinterpret_cast<uintptr_t>(bon)) & 15) == 0;
+    const float at = KIND == 1 ? expf(a.decay[t * a.ldd + h]) : a_const;
+    float vj = live ? a.v[t * a.ldv + (int64_t)h * a.dv + j] : 0.f;
+    if (a.vscale != nullptr) vj *= a.vscale[t * a.ldvs + h];
+    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int g = 0; g < KPT; g += 4) {
+      const float4 q4 = ld4(qp, i0 + g, dk, vq), k4 = ld4(kp, i0 + g, dk, vq);
+      float4 d4 = make_float4(at, at, at, at), u4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (KIND == 2) { d4 = ld4(dpp, i0 + g, dk, vq); d4 = make_float4(expf(d4.x), expf(d4.y), expf(d4.z), expf(d4.w)); }
+      if (READ_BEFORE && bon != nullptr) u4 = ld4(bon, i0 + g, dk, vq);
+      const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w},
+                  uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x = kk[e] * vj;
+        float& acc = (e & 1) ? acc1 : acc0;
+        if (READ_BEFORE) {
+          acc = fmaf(qq[e], fmaf(uu[e], x, S[g + e]), acc);
+          S[g + e] = fmaf(dd[e], S[g + e], x);
+        } else {
+          S[g + e] = fmaf(dd[e], S[g + e], x);
+          acc = fmaf(qq[e], S[g + e], acc);
+        }
+      }
+    }
+    float acc = acc0 + acc1;
+    for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (live) {
+      if (r == 0) a.out[t * a.H * a.dv + (int64_t)h * a.dv + j] = acc;
+      store_col(sp);
+    }
+    return;
+  }
   for (int c0 = t_lo; c0 < t_hi; c0 += TCH) {
     const int nt = min(TCH, t_hi - c0);
     __syncthreads();
     for (int tt = warp; tt < nt; tt += nwarp) {
       const int64_t t = s.q0 + c0 + tt;
       for (int i = lane; i < R * KPT; i += 32) {
-        const int p = tt * row + (i >> 4) * STRIP + (i & 15);
+        const int p = tt * row + (i / KPT) * STRIP + (i % KPT);
         const bool in = i < dk;
+        const float kx = in ? a.k[t * a.ldk + (int64_t)hq * dk + i] : 0.f;
         if (MODE != 1) qs[p] = in ? a.q[t * a.ldq + (int64_t)hq * dk + i] : 0.f;
-        ks[p] = in ? a.k[t * a.ldk + (int64_t)hq * dk + i] : 0.f;
+        ks[p] = kx;
         if (KIND == 2) as[p] = in ? expf(a.decay[t * a.ldd + (int64_t)h * dk + i]) : 0.f;
+        if (READ_BEFORE && MODE != 1) us[p] = (in && bon != nullptr) ? bon[i] * kx : 0.f;
       }
       const float sc = a.vscale != nullptr ? a.vscale[t * a.ldvs + h] : 1.f;
       for (int jj = lane; jj < nj; jj += 32) vs[tt * a.dvt + jj] = a.v[t * a.ldv + (int64_t)h * a.dv + j0 + jj] * sc;
       if (KIND == 1 && lane == 0) as[tt] = expf(a.decay[t * a.ldd + h]);
     }
     __syncthreads();
-#pragma unroll 2
+#pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const float vj = live ? vs[tt * a.dvt + jl] : 0.f;
       const float at = KIND == 1 ? as[tt] : a_const;
       const float4* q4 = reinterpret_cast<const float4*>(qs + tt * row + r * STRIP);
       const float4* k4 = reinterpret_cast<const float4*>(ks + tt * row + r * STRIP);
       const float4* a4 = reinterpret_cast<const float4*>(as + tt * row + r * STRIP);
-      float acc0 = 0.f, acc1 = 0.f;
+      const float4* u4 = reinterpret_cast<const float4*>(us + tt * row + r * STRIP);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (KIND != 2 && MODE == 1) dps *= at;
 #pragma unroll
       for (int g = 0; g < KPT / 4; ++g) {
         const float4 kv4 = k4[g];
-        float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), dv4 = make_float4(at, at, at, at);
+        float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), dv4 = make_float4(at, at, at, at), uv = make_float4(0.f, 0.f, 0.f, 0.f);
         if (MODE != 1) qv = q4[g];
         if (KIND == 2) dv4 = a4[g];
-        const float qq[4] = {qv.x, qv.y, qv.z, qv.w}, kk[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
+        if (READ_BEFORE && MODE != 1) uv = u4[g];
+        const float qq[4] = {qv.x, qv.y, qv.z, qv.w}, kk[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w},
+                    uu[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = g * 4 + e;
           const float kv = kk[e] * vj;
-          float& acc = (e & 1) ? acc1 : acc0;
           if (MODE == 1) {
             S[ii] = fmaf(dd[e], S[ii], kv);
-            dp[ii] *= dd[e];
+            if (KIND == 2) dp[KIND == 2 && MODE == 1 ? ii : 0] *= dd[e];
           } else if (READ_BEFORE) {
-            acc = fmaf(qq[e], fmaf(u[ii], kv, S[ii]), acc);
+            acc[e] = fmaf(qq[e], fmaf(uu[e], vj, S[ii]), acc[e]);     // uu = bonus * k
             S[ii] = fmaf(dd[e], S[ii], kv);
           } else {
             S[ii] = fmaf(dd[e], S[ii], kv);
-            acc = fmaf(qq[e], S[ii], acc);
+            acc[e] = fmaf(qq[e], S[ii], acc[e]);
           }
         }
       }
       if (MODE != 1) {
-        float acc = acc0 + acc1;
-        for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (live && r == 0) a.out[(int64_t)(s.q0 + c0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = acc;
+        float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        for (int w = 1; w < R; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+        if (live && r == 0) a.out[(int64_t)(s.q0 + c0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = o;
       }
     }
   }
   if (MODE == 1) {
     const int64_t cb = ((int64_t)blockIdx.x * a.nch + ch) * a.H + h;
-    if (live) store16(a.chunk_state + (cb * a.dv + col) * dk, S);
-    if (slice == 0 && jl == 0) store16(a.chunk_decay + cb * dk, dp);   // rows beyond dk hold zeros: never stored
+    if (live) store_col(a.chunk_state + (cb * a.dv + col) * dk);
+    if (slice == 0 && jl == 0) {
+      float* cd = a.chunk_decay + cb * dk;
+#pragma unroll
+      for (int g = 0; g < KPT; g += 4) {
+        if (KIND == 2) st4(cd, i0 + g, dk, vec, dp[KIND == 2 && MODE == 1 ? g : 0], dp[KIND == 2 && MODE == 1 ? g + 1 : 0],
+                           dp[KIND == 2 && MODE == 1 ? g + 2 : 0], dp[KIND == 2 && MODE == 1 ? g + 3 : 0]);
+        else st4(cd, i0 + g, dk, vec, dps, dps, dps, dps);
+      }
+    }
   } else if (live && last_chunk) {
-    store16(sp, S);
+    store_col(sp);
   }
 }
 
@@ -465,7 +535,8 @@ LLMSS_API int llmss_token_shift(const float* x, int64_t ldx, const float* mu, in
                                 const int* seq_lens, const int* slots, int B, int max_q, float* prev_state, int dtype,
                                 cudaStream_t stream) {
   if (B <= 0 || T_ <= 0) return 0;
-  const dim3 grid(B, max(1, min(max_q, 256)));
+  // a decode batch has one row per sequence: spread its columns over blocks instead
+  const dim3 grid(B, max(1, min(max_q, 256)), max_q < 8 ? max(1, min((W + 255) / 256, 32)) : 1);
   LLMSS_BY_DTYPE(dtype, (token_shift_kernel<T><<<grid, 128, 0, stream>>>(x, ldx, mu, S, (T*)out, (int64_t)T_, W, cu_q, seq_lens, slots,
                                                                          prev_state)));
   LLMSS_CHECK_CUDA(cudaGetLastError());
@@ -516,7 +587,7 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
                                 int B, int heads, int qk_heads, int dk, int dv, int read_before, float* scratch, int chunk,
                                 int max_q, cudaStream_t stream) {
   LLMSS_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "linear_scan: %d heads over %d q/k heads", heads, qk_heads);
-  LLMSS_REQUIRE(dk > 0 && dk <= 32 * KPT, "linear_scan: key size %d (at most %d)", dk, 32 * KPT);
+  LLMSS_REQUIRE(dk > 0 && dk <= 1024, "linear_scan: key size %d (at most 1024)", dk);
   LLMSS_REQUIRE(decay_kind >= 0 && decay_kind <= 2, "linear_scan: decay kind %d", decay_kind);
   LLMSS_REQUIRE(chunk == 0 || (chunk % TCH == 0 && scratch != nullptr && max_q > 0), "linear_scan: bad chunking (%d tokens)", chunk);
   if (B <= 0) return 0;
@@ -524,8 +595,9 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
   a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.decay = decay; a.ldd = ldd; a.bonus = bonus;
   a.vscale = vscale; a.ldvs = ldvs; a.out = out; a.state = state; a.cu_q = cu_q; a.seq_lens = seq_lens; a.slots = slots;
   a.H = heads; a.rep = heads / qk_heads; a.dk = dk; a.dv = dv;
-  a.R = pow2_at_least((dk + KPT - 1) / KPT);
-  a.dvt = min(dv, SCAN_THREADS / a.R);
+  const int kpt = dk >= 48 ? 64 : 16;           // key rows per thread
+  a.R = pow2_at_least((dk + kpt - 1) / kpt);
+  a.dvt = min(dv, (kpt == 64 ? 128 : SCAN_THREADS) / a.R);
   a.chunk = chunk;
   a.nch = chunk > 0 ? (max_q + chunk - 1) / chunk : 1;
   // few blocks (a prompt round of few sequences): narrower value slices until the grid covers the SMs a few times over
@@ -535,15 +607,20 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
   a.chunk_state = scratch != nullptr ? scratch + (int64_t)B * heads * dv * dk : nullptr;
   a.chunk_decay = scratch != nullptr ? a.chunk_state + (int64_t)B * a.nch * heads * dv * dk : nullptr;
   const int threads = ((a.dvt * a.R + 31) / 32) * 32;
-  const int row = a.R * STRIP;
-  const size_t smem = sizeof(float) * ((size_t)TCH * row * 2 + (decay_kind == 2 ? (size_t)TCH * row : TCH) + (size_t)TCH * a.dvt);
+  const int row = a.R * (kpt + 4);
+  const size_t smem = sizeof(float) * ((size_t)TCH * row * 2 + (decay_kind == 2 ? (size_t)TCH * row : TCH) +
+                                       (read_before ? (size_t)TCH * row : 0) + (size_t)TCH * a.dvt);
   const dim3 grid(B, heads, a.nslices * (chunk > 0 ? a.nch : 1));
   LLMSS_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear_scan: grid too large");
-#define LLMSS_SCAN1(RB, KIND, MODE)                                                            \
+#define LLMSS_SCAN2(RB, KIND, MODE, KP)                                                        \
   do {                                                                                         \
     static PerDeviceSmem g;                                                                    \
-    LLMSS_CHECK_CUDA(g.ensure(linear_scan_kernel<RB, KIND, MODE>, (int)smem));                 \
-    linear_scan_kernel<RB, KIND, MODE><<<grid, threads, smem, stream>>>(a);                    \
+    LLMSS_CHECK_CUDA(g.ensure(linear_scan_kernel<RB, KIND, MODE, KP>, (int)smem));             \
+    linear_scan_kernel<RB, KIND, MODE, KP><<<grid, threads, smem, stream>>>(a);                \
+  } while (0)
+#define LLMSS_SCAN1(RB, KIND, MODE)                                                            \
+  do {                                                                                         \
+    if (kpt == 64) LLMSS_SCAN2(RB, KIND, MODE, 64); else LLMSS_SCAN2(RB, KIND, MODE, 16);      \
   } while (0)
 #define LLMSS_SCAN(RB, KIND)                                                                   \
   do {                                                                                         \
@@ -557,6 +634,7 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
   }
 #undef LLMSS_SCAN
 #undef LLMSS_SCAN1
+#undef LLMSS_SCAN2
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
