@@ -450,6 +450,273 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(ScanArgs a) {
   }
 }
 
+// The same recurrence with a two-dimensional register tile: a thread owns 8 key rows x 8 value columns of the state, so the
+// 8 + 8 (+ 8 + 8) staged values it reads per token feed 64 state elements (the column-per-thread form above reads one
+// staged value per element and is bound by shared-memory wavefronts).  RG row groups of 8 (8 for key sizes up to 64, 16 up
+// to 128) are adjacent lanes; an output column is finished by a reduce-scatter over those lanes (4 + 2 + 1 shuffles leave
+// lane g with column g), so a warp's stores are 32 consecutive outputs.  Same passes (MODE) and state layout as above.
+constexpr int TSTR = 12;    // floats between the staged 8-row groups of a token: the 8 groups a quarter warp reads lie in different banks
+
+template <bool READ_BEFORE, int KIND, int MODE, int RG>
+__global__ void __launch_bounds__(128) linear_scan_tile_kernel(ScanArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  const Seq s = seq_of(a.cu_q, a.seq_lens, a.slots, blockIdx.x);
+  if (s.ql == 0) return;
+  const int h = blockIdx.y;
+  const int slice = MODE == 0 ? blockIdx.z : blockIdx.z % a.nslices, ch = MODE == 0 ? 0 : blockIdx.z / a.nslices;
+  const int j0 = slice * a.dvt;
+  const int t_lo = MODE == 0 ? 0 : ch * a.chunk, t_hi = MODE == 0 ? s.ql : min(s.ql, t_lo + a.chunk);
+  if (t_lo >= s.ql) return;
+  const bool last_chunk = MODE == 0 || t_hi == s.ql;
+  const int nj = min(a.dvt, a.dv - j0);          // value columns of this block
+  const int dk = a.dk;
+  constexpr int row = RG * TSTR;                 // floats per staged token
+  const int cg = threadIdx.x / RG, rg = threadIdx.x % RG;
+  const int i0 = rg * 8, c0 = cg * 8;            // first key row / first column (inside the slice) of this thread
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float* qs = sm;
+  float* ks = qs + TCH * row;
+  float* as = ks + TCH * row;                                   // [TCH][row] (kind 2) or [TCH] (kind 1)
+  float* us = as + (KIND == 2 ? TCH * row : TCH);               // bonus * k (READ_BEFORE)
+  float* vs = us + (READ_BEFORE ? TCH * row : 0);               // [TCH][dvt]
+  float S[8][8], dp[8];
+  float dps = 1.f;
+  const bool vec = (dk & 3) == 0;
+  const int64_t bh = (int64_t)blockIdx.x * a.H + h;
+  float* sp = a.state + ((int64_t)s.slot * a.H + h) * a.dv * dk;           // this head's [dv][dk]
+  auto load_tile = [&](const float* base, bool on) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const bool ok = on && c0 + c < nj;
+      const float* p = base + (int64_t)(j0 + c0 + c) * dk;
+      const float4 x = ok ? ld4(p, i0, dk, vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 y = ok ? ld4(p, i0 + 4, dk, vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[0][c] = x.x; S[1][c] = x.y; S[2][c] = x.z; S[3][c] = x.w; S[4][c] = y.x; S[5][c] = y.y; S[6][c] = y.z; S[7][c] = y.w;
+    }
+  };
+  auto store_tile = [&](float* base) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (c0 + c >= nj) continue;
+      float* p = base + (int64_t)(j0 + c0 + c) * dk;
+      st4(p, i0, dk, vec, S[0][c], S[1][c], S[2][c], S[3][c]);
+      st4(p, i0 + 4, dk, vec, S[4][c], S[5][c], S[6][c], S[7][c]);
+    }
+  };
+  if (MODE == 0) {
+    load_tile(sp, s.ctx > 0);
+  } else if (MODE == 1) {
+    if (ch == 0) {
+      load_tile(sp, s.ctx > 0);
+      store_tile(a.old_copy + bh * a.dv * dk);
+    }
+    if (last_chunk) return;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      dp[r] = 1.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) S[r][c] = 0.f;
+    }
+  } else {
+    load_tile(a.old_copy + bh * a.dv * dk, true);
+    for (int cc = 0; cc < ch; ++cc) {
+      const int64_t cb = ((int64_t)blockIdx.x * a.nch + cc) * a.H + h;
+      const float* cs = a.chunk_state + cb * a.dv * dk;
+      const float* cd = a.chunk_decay + cb * dk;
+      const float4 d0 = ld4(cd, i0, dk, vec), d1 = ld4(cd, i0 + 4, dk, vec);
+      const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c0 + c >= nj) continue;
+        const float* p = cs + (int64_t)(j0 + c0 + c) * dk;
+        const float4 x = ld4(p, i0, dk, vec), y = ld4(p, i0 + 4, dk, vec);
+        const float sl[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int r = 0; r < 8; ++r) S[r][c] = fmaf(d[r], S[r][c], sl[r]);
+      }
+    }
+  }
+  const float a_const = KIND == 0 ? a.decay[h] : 0.f;
+  const int hq = h / a.rep;
+  const float* bon = (READ_BEFORE && a.bonus != nullptr) ? a.bonus + (int64_t)h * dk : nullptr;
+  // one token: q / k / decay / bonus * k rows and the scaled value columns of this thread in registers -> outputs
+  auto step = [&](const float (&qq)[8], const float (&kk)[8], const float (&dd)[8], const float (&uk)[8], const float (&vv)[8],
+                  int64_t t) {
+    float acc[8];
+    float quk = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+    if (READ_BEFORE && MODE != 1) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) quk = fmaf(qq[r], uk[r], quk);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (MODE == 1) {
+          S[r][c] = fmaf(dd[r], S[r][c], kk[r] * vv[c]);
+        } else if (READ_BEFORE) {
+          acc[c] = fmaf(qq[r], S[r][c], acc[c]);
+          S[r][c] = fmaf(dd[r], S[r][c], kk[r] * vv[c]);
+        } else {
+          S[r][c] = fmaf(dd[r], S[r][c], kk[r] * vv[c]);
+          acc[c] = fmaf(qq[r], S[r][c], acc[c]);
+        }
+      }
+      if (MODE == 1 && KIND == 2) dp[r] *= dd[r];
+    }
+    if (MODE == 1) return;
+    if (READ_BEFORE) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] = fmaf(vv[c], quk, acc[c]);       // the current token's bonus term
+    }
+    if (RG == 16) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 8);
+    }
+    // reduce-scatter over the 8 lanes of a column group: lane g ends with column g
+    float b4[4], b2[2];
+    const bool hi4 = rg & 4, hi2 = rg & 2, hi1 = rg & 1;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float give = hi4 ? acc[c] : acc[c + 4];
+      b4[c] = (hi4 ? acc[c + 4] : acc[c]) + __shfl_xor_sync(0xffffffffu, give, 4);
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const float give = hi2 ? b4[c] : b4[c + 2];
+      b2[c] = (hi2 ? b4[c + 2] : b4[c]) + __shfl_xor_sync(0xffffffffu, give, 2);
+    }
+    const float give = hi1 ? b2[0] : b2[1];
+    const float o = (hi1 ? b2[1] : b2[0]) + __shfl_xor_sync(0xffffffffu, give, 1);
+    const int c = rg & 7;
+    if ((RG == 8 || rg < 8) && c0 + c < nj) a.out[t * a.H * a.dv + (int64_t)h * a.dv + j0 + c0 + c] = o;
+  };
+  if (MODE == 0 && s.ql == 1) {   // a decode step: straight from global memory, no staging, no barrier
+    const int64_t t = s.q0;
+    const float* qp = a.q + t * a.ldq + (int64_t)hq * dk;
+    const float* kp = a.k + t * a.ldk + (int64_t)hq * dk;
+    const float* dpp = KIND == 2 ? a.decay + t * a.ldd + (int64_t)h * dk : nullptr;
+    const float* vp = a.v + t * a.ldv + (int64_t)h * a.dv + j0;
+    const bool vq = vec && ((reinterpret_cast<uintptr_t>(qp) | reinterpret_cast<uintptr_t>(kp) | reinterpret_cast<uintptr_t>(dpp) |
+                             reinterpret_cast<uintptr_t>(bon)) & 15) == 0;
+    const bool vv4 = (reinterpret_cast<uintptr_t>(vp) & 15) == 0;
+    const float at = KIND == 1 ? expf(a.decay[t * a.ldd + h]) : a_const;
+    const float sc = a.vscale != nullptr ? a.vscale[t * a.ldvs + h] : 1.f;
+    float qq[8], kk[8], dd[8], uk[8], vv[8];
+    const float4 q0 = ld4(qp, i0, dk, vq), q1 = ld4(qp, i0 + 4, dk, vq), k0 = ld4(kp, i0, dk, vq), k1 = ld4(kp, i0 + 4, dk, vq);
+    const float4 v0 = ld4(vp, c0, nj, vv4), v1 = ld4(vp, c0 + 4, nj, vv4);
+    const float qa[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w}, ka[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+    const float va[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float da[8] = {at, at, at, at, at, at, at, at}, ua[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (KIND == 2) {
+      const float4 x = ld4(dpp, i0, dk, vq), y = ld4(dpp, i0 + 4, dk, vq);
+      da[0] = expf(x.x); da[1] = expf(x.y); da[2] = expf(x.z); da[3] = expf(x.w);
+      da[4] = i0 + 4 < dk ? expf(y.x) : 0.f; da[5] = expf(y.y); da[6] = expf(y.z); da[7] = expf(y.w);
+    }
+    if (READ_BEFORE && bon != nullptr) {
+      const float4 x = ld4(bon, i0, dk, vq), y = ld4(bon, i0 + 4, dk, vq);
+      ua[0] = x.x; ua[1] = x.y; ua[2] = x.z; ua[3] = x.w; ua[4] = y.x; ua[5] = y.y; ua[6] = y.z; ua[7] = y.w;
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) { qq[r] = qa[r]; kk[r] = ka[r]; dd[r] = da[r]; uk[r] = ua[r] * ka[r]; vv[r] = va[r] * sc; }
+    step(qq, kk, dd, uk, vv, t);
+    store_tile(sp);
+    return;
+  }
+  const float* qbase = a.q + (int64_t)hq * dk;
+  const float* kbase = a.k + (int64_t)hq * dk;
+  const float* dbase = KIND == 2 ? a.decay + (int64_t)h * dk : nullptr;
+  const float* vbase = a.v + (int64_t)h * a.dv + j0;
+  // whole 16-byte vectors of q / k / decay / bonus rows: the row count, the row strides and the bases allow it
+  const bool in_vec = vec && ((a.ldq | a.ldk | (KIND == 2 ? a.ldd : 0)) & 3) == 0 &&
+                      ((reinterpret_cast<uintptr_t>(qbase) | reinterpret_cast<uintptr_t>(kbase) | reinterpret_cast<uintptr_t>(dbase) |
+                        reinterpret_cast<uintptr_t>(bon)) & 15) == 0;
+  for (int t0 = t_lo; t0 < t_hi; t0 += TCH) {
+    const int nt = min(TCH, t_hi - t0);
+    __syncthreads();
+    // flattened over (token, row) so that a thread's loads are independent and many are in flight at once; 16-byte loads
+    // where the rows allow
+    if (in_vec) {
+#pragma unroll 4
+      for (int idx = threadIdx.x; idx < nt * (RG * 2); idx += blockDim.x) {
+        const int tt = idx / (RG * 2), i = (idx % (RG * 2)) * 4;
+        const int p = tt * row + (i >> 3) * TSTR + (i & 7);
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        const bool in = i < dk;                    // dk is a multiple of 4 here: whole vectors
+        const int64_t t = s.q0 + t0 + tt;
+        const float4 k4 = in ? *reinterpret_cast<const float4*>(kbase + t * a.ldk + i) : z;
+        if (MODE != 1) *reinterpret_cast<float4*>(qs + p) = in ? *reinterpret_cast<const float4*>(qbase + t * a.ldq + i) : z;
+        *reinterpret_cast<float4*>(ks + p) = k4;
+        if (KIND == 2) {
+          const float4 d4 = in ? *reinterpret_cast<const float4*>(dbase + t * a.ldd + i) : z;
+          *reinterpret_cast<float4*>(as + p) = in ? make_float4(expf(d4.x), expf(d4.y), expf(d4.z), expf(d4.w)) : z;
+        }
+        if (READ_BEFORE && MODE != 1) {
+          const float4 b4 = (in && bon != nullptr) ? *reinterpret_cast<const float4*>(bon + i) : z;
+          *reinterpret_cast<float4*>(us + p) = make_float4(b4.x * k4.x, b4.y * k4.y, b4.z * k4.z, b4.w * k4.w);
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int idx = threadIdx.x; idx < nt * (RG * 8); idx += blockDim.x) {
+        const int tt = idx / (RG * 8), i = idx % (RG * 8);
+        const int64_t t = s.q0 + t0 + tt;
+        const int p = tt * row + (i >> 3) * TSTR + (i & 7);
+        const bool in = i < dk;
+        const float kx = in ? kbase[t * a.ldk + i] : 0.f;
+        if (MODE != 1) qs[p] = in ? qbase[t * a.ldq + i] : 0.f;
+        ks[p] = kx;
+        if (KIND == 2) as[p] = in ? expf(dbase[t * a.ldd + i]) : 0.f;
+        if (READ_BEFORE && MODE != 1) us[p] = (in && bon != nullptr) ? bon[i] * kx : 0.f;
+      }
+    }
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < nt * a.dvt; idx += blockDim.x) {
+      const int tt = idx / a.dvt, jj = idx % a.dvt;
+      const int64_t t = s.q0 + t0 + tt;
+      const float sc = a.vscale != nullptr ? a.vscale[t * a.ldvs + h] : 1.f;
+      vs[idx] = jj < nj ? vbase[t * a.ldv + jj] * sc : 0.f;
+    }
+    if (KIND == 1 && threadIdx.x < nt) as[threadIdx.x] = expf(a.decay[(int64_t)(s.q0 + t0 + threadIdx.x) * a.ldd + h]);
+    __syncthreads();
+#pragma unroll 1
+    for (int tt = 0; tt < nt; ++tt) {
+      const float at = KIND == 1 ? as[tt] : a_const;
+      if (KIND != 2 && MODE == 1) dps *= at;
+      float qq[8], kk[8], dd[8], uk[8], vv[8];
+      const int p = tt * row + rg * TSTR;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + p + 4 * g);
+        const float4 v4 = *reinterpret_cast<const float4*>(vs + tt * a.dvt + c0 + 4 * g);
+        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = make_float4(at, at, at, at), u4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE != 1) q4 = *reinterpret_cast<const float4*>(qs + p + 4 * g);
+        if (KIND == 2) d4 = *reinterpret_cast<const float4*>(as + p + 4 * g);
+        if (READ_BEFORE && MODE != 1) u4 = *reinterpret_cast<const float4*>(us + p + 4 * g);
+        kk[4 * g] = k4.x; kk[4 * g + 1] = k4.y; kk[4 * g + 2] = k4.z; kk[4 * g + 3] = k4.w;
+        vv[4 * g] = v4.x; vv[4 * g + 1] = v4.y; vv[4 * g + 2] = v4.z; vv[4 * g + 3] = v4.w;
+        qq[4 * g] = q4.x; qq[4 * g + 1] = q4.y; qq[4 * g + 2] = q4.z; qq[4 * g + 3] = q4.w;
+        dd[4 * g] = d4.x; dd[4 * g + 1] = d4.y; dd[4 * g + 2] = d4.z; dd[4 * g + 3] = d4.w;
+        uk[4 * g] = u4.x; uk[4 * g + 1] = u4.y; uk[4 * g + 2] = u4.z; uk[4 * g + 3] = u4.w;
+      }
+      step(qq, kk, dd, uk, vv, s.q0 + t0 + tt);
+    }
+  }
+  if (MODE == 1) {
+    const int64_t cb = ((int64_t)blockIdx.x * a.nch + ch) * a.H + h;
+    store_tile(a.chunk_state + cb * a.dv * dk);
+    if (slice == 0 && cg == 0) {
+      float* cd = a.chunk_decay + cb * dk;
+      if (KIND == 2) { st4(cd, i0, dk, vec, dp[0], dp[1], dp[2], dp[3]); st4(cd, i0 + 4, dk, vec, dp[4], dp[5], dp[6], dp[7]); }
+      else { st4(cd, i0, dk, vec, dps, dps, dps, dps); st4(cd, i0 + 4, dk, vec, dps, dps, dps, dps); }
+    }
+  } else if (last_chunk) {
+    store_tile(sp);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ gated_rmsnorm
 struct GnArgs {
   const float* o; int64_t ldo;
@@ -574,6 +841,10 @@ LLMSS_API int llmss_ssm_dt(const float* raw, int64_t ldr, const float* dt_bias, 
   return 0;
 }
 
+static int g_scan_tile = 1;
+// 0: every key size runs the column-per-thread kernel (A/B aid and the form tests compare against)
+LLMSS_API int llmss_linear_scan_set_tile(int on) { g_scan_tile = on; return 0; }
+
 LLMSS_API int64_t llmss_linear_scan_scratch_floats(int B, int heads, int dk, int dv, int max_q, int chunk) {
   const int nch = chunk > 0 ? (max_q + chunk - 1) / chunk : 0;
   return (int64_t)B * heads * ((int64_t)dv * dk + (int64_t)nch * ((int64_t)dv * dk + dk));
@@ -595,6 +866,50 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
   a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.decay = decay; a.ldd = ldd; a.bonus = bonus;
   a.vscale = vscale; a.ldvs = ldvs; a.out = out; a.state = state; a.cu_q = cu_q; a.seq_lens = seq_lens; a.slots = slots;
   a.H = heads; a.rep = heads / qk_heads; a.dk = dk; a.dv = dv;
+  a.chunk = chunk;
+  a.nch = chunk > 0 ? (max_q + chunk - 1) / chunk : 1;
+  a.old_copy = scratch;
+  a.chunk_state = scratch != nullptr ? scratch + (int64_t)B * heads * dv * dk : nullptr;
+  a.chunk_decay = scratch != nullptr ? a.chunk_state + (int64_t)B * a.nch * heads * dv * dk : nullptr;
+  if (dk > 32 && dk <= 128 && g_scan_tile) {
+    // 8 x 8 register tiles: RG row groups of 8 key rows, value columns in groups of 8
+    const int rg = dk <= 64 ? 8 : 16;
+    a.R = rg;
+    a.dvt = min((dv + 7) / 8 * 8, 8 * (128 / rg));
+    while ((int64_t)B * heads * a.nch * ((dv + a.dvt - 1) / a.dvt) < 4 * 148 && a.dvt > 8 && (a.dvt / 2) % 8 == 0 && (a.dvt / 16) * rg >= 32) a.dvt /= 2;
+    a.nslices = (dv + a.dvt - 1) / a.dvt;
+    const int threads = (a.dvt / 8) * rg;
+    const int row = rg * TSTR;
+    const size_t smem = sizeof(float) * ((size_t)TCH * row * 2 + (decay_kind == 2 ? (size_t)TCH * row : TCH) +
+                                         (read_before ? (size_t)TCH * row : 0) + (size_t)TCH * a.dvt);
+    const dim3 grid(B, heads, a.nslices * (chunk > 0 ? a.nch : 1));
+    LLMSS_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "linear_scan: grid too large");
+#define LLMSS_TILE2(RB, KIND, MODE, RG_)                                                       \
+  do {                                                                                         \
+    static PerDeviceSmem g;                                                                    \
+    LLMSS_CHECK_CUDA(g.ensure(linear_scan_tile_kernel<RB, KIND, MODE, RG_>, (int)smem));       \
+    linear_scan_tile_kernel<RB, KIND, MODE, RG_><<<grid, threads, smem, stream>>>(a);          \
+  } while (0)
+#define LLMSS_TILE1(RB, KIND, MODE)                                                            \
+  do {                                                                                         \
+    if (rg == 8) LLMSS_TILE2(RB, KIND, MODE, 8); else LLMSS_TILE2(RB, KIND, MODE, 16);         \
+  } while (0)
+#define LLMSS_TILE(RB, KIND)                                                                   \
+  do {                                                                                         \
+    if (chunk > 0) { LLMSS_TILE1(RB, KIND, 1); LLMSS_TILE1(RB, KIND, 2); }                     \
+    else LLMSS_TILE1(RB, KIND, 0);                                                             \
+  } while (0)
+    if (read_before) {
+      if (decay_kind == 0) LLMSS_TILE(true, 0); else if (decay_kind == 1) LLMSS_TILE(true, 1); else LLMSS_TILE(true, 2);
+    } else {
+      if (decay_kind == 0) LLMSS_TILE(false, 0); else if (decay_kind == 1) LLMSS_TILE(false, 1); else LLMSS_TILE(false, 2);
+    }
+#undef LLMSS_TILE
+#undef LLMSS_TILE1
+#undef LLMSS_TILE2
+    LLMSS_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   const int kpt = dk >= 48 ? 64 : 16;           // key rows per thread
   a.R = pow2_at_least((dk + kpt - 1) / kpt);
   a.dvt = min(dv, (kpt == 64 ? 128 : SCAN_THREADS) / a.R);
