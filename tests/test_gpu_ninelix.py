@@ -221,3 +221,27 @@ def test_model_on_the_tensor_core_attention(tmp_path):
     cases.test_whole_prompt_and_residual_stream(tmp_path / "a", "tc_sizes", "cuda", BF16, 8e-2)
     cases.test_decode_token_by_token_and_portions(tmp_path / "b", "tc_sizes", "cuda", BF16, 8e-2)
     cases.test_whole_prompt_and_residual_stream(tmp_path / "c", "tc_sizes", "cuda", F32, 3e-4)
+
+
+cases.CONFIGS["long"] = ninelix_config(128, 199, [
+    {"type": "wkv", "heads": 2, "dim": 64, "lora": 8, "mlp": None},
+    {"type": "parallel", "left": cases.attn(heads=4, kv_heads=2, dim=64, vdim=64, conv=3, bias_max=300, buckets=16),
+     "right": cases.ssd(heads=4, vdim=24, state=40, groups=2, norm_groups=2, conv=4), "mlp": {"kind": "dense", "ff": 128}},
+    {"type": "lightning", "heads": 2, "dim": 128, "vdim": 72, "mlp": None},
+    {"type": "parallel", "left": cases.attn(heads=3, kv_heads=1, dim=40, vdim=24, conv=2, bias_max=900, buckets=24),
+     "right": cases.ssd(heads=2, vdim=64, state=128, groups=1, norm_groups=1, conv=2), "mlp": None}], buckets=53)
+
+
+@pytest.mark.parametrize("dtype,tol", [pytest.param(F32, 5e-4, id="f32"), pytest.param(BF16, 0.12, id="bf16")])
+def test_long_prompt_in_portions_equals_the_cpu_engine(tmp_path, dtype, tol):
+    """700 tokens: portions long enough for the two-pass recurrence (and one just under its threshold), a single token between
+    them, attention over a dozen pages with the distance table ending inside and beyond the context -- against the same model
+    on the CPU ops fed in one piece."""
+    cfg, W, cpu = cases.build(tmp_path / "a", "long", "cpu", F32, max_seq_len=1024)
+    _, _, gpu = cases.build(tmp_path / "b", "long", "cuda", dtype, max_seq_len=1024)
+    toks = cases.tokens_for(cfg, 700, 21)
+    want = cases.feed_in_portions(cpu, "w", toks, [700])
+    got = cases.feed_in_portions(gpu, "p", toks, [300, 1, 257, 142])
+    cases.close(got, want, tol)
+    got = cases.feed_in_portions(gpu, "q", toks, [255, 445])
+    cases.close(got, want, tol)
