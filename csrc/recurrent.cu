@@ -633,9 +633,68 @@ __global__ void __launch_bounds__(128) linear_scan_tile_kernel(ScanArgs a) {
   const bool in_vec = vec && ((a.ldq | a.ldk | (KIND == 2 ? a.ldd : 0)) & 3) == 0 &&
                       ((reinterpret_cast<uintptr_t>(qbase) | reinterpret_cast<uintptr_t>(kbase) | reinterpret_cast<uintptr_t>(dbase) |
                         reinterpret_cast<uintptr_t>(bon)) & 15) == 0;
+  // Register prefetch: the next stage's rows are fetched (16-byte loads, up to four per array and thread) before the current
+  // stage's tokens are computed and written to shared memory after them, so their latency hides behind the arithmetic.
+  const int nthr = blockDim.x;
+  const bool v_vec = (a.dvt & 3) == 0 && nj == a.dvt && (a.ldv & 3) == 0 && (reinterpret_cast<uintptr_t>(vbase) & 15) == 0;
+  const bool pf = in_vec && v_vec && nthr * 4 >= TCH * RG * 2 && nthr * 16 >= TCH * a.dvt;
+  float4 rq[4], rk[4], rd[4], rv[4];
+  float rdec = 0.f;
+  auto fetch = [&](int t0n, int ntn) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = threadIdx.x + u * nthr;
+      rq[u] = rk[u] = rd[u] = rv[u] = z;
+      if (idx < ntn * (RG * 2)) {
+        const int tt = idx / (RG * 2), i = (idx % (RG * 2)) * 4;
+        const int64_t t = s.q0 + t0n + tt;
+        if (i < dk) {
+          rk[u] = *reinterpret_cast<const float4*>(kbase + t * a.ldk + i);
+          if (MODE != 1) rq[u] = *reinterpret_cast<const float4*>(qbase + t * a.ldq + i);
+          if (KIND == 2) rd[u] = *reinterpret_cast<const float4*>(dbase + t * a.ldd + i);
+        }
+      }
+      if (idx < ntn * (a.dvt >> 2)) {
+        const int tt = idx / (a.dvt >> 2), jj = (idx % (a.dvt >> 2)) * 4;
+        const int64_t t = s.q0 + t0n + tt;
+        const float sc = a.vscale != nullptr ? a.vscale[t * a.ldvs + h] : 1.f;
+        const float4 x = *reinterpret_cast<const float4*>(vbase + t * a.ldv + jj);
+        rv[u] = make_float4(x.x * sc, x.y * sc, x.z * sc, x.w * sc);
+      }
+    }
+    if (KIND == 1 && threadIdx.x < ntn) rdec = a.decay[(int64_t)(s.q0 + t0n + threadIdx.x) * a.ldd + h];
+  };
+  auto commit = [&](int ntn) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = threadIdx.x + u * nthr;
+      if (idx < ntn * (RG * 2)) {
+        const int tt = idx / (RG * 2), i = (idx % (RG * 2)) * 4;
+        const int p = tt * row + (i >> 3) * TSTR + (i & 7);
+        const bool in = i < dk;
+        if (MODE != 1) *reinterpret_cast<float4*>(qs + p) = rq[u];
+        *reinterpret_cast<float4*>(ks + p) = rk[u];
+        if (KIND == 2) *reinterpret_cast<float4*>(as + p) = in ? make_float4(expf(rd[u].x), expf(rd[u].y), expf(rd[u].z), expf(rd[u].w))
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (READ_BEFORE && MODE != 1) {
+          const float4 b4 = (in && bon != nullptr) ? *reinterpret_cast<const float4*>(bon + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          *reinterpret_cast<float4*>(us + p) = make_float4(b4.x * rk[u].x, b4.y * rk[u].y, b4.z * rk[u].z, b4.w * rk[u].w);
+        }
+      }
+      if (idx < ntn * (a.dvt >> 2)) *reinterpret_cast<float4*>(vs + idx * 4) = rv[u];
+    }
+    if (KIND == 1 && threadIdx.x < ntn) as[threadIdx.x] = expf(rdec);
+  };
+  if (pf) fetch(t_lo, min(TCH, t_hi - t_lo));
   for (int t0 = t_lo; t0 < t_hi; t0 += TCH) {
     const int nt = min(TCH, t_hi - t0);
     __syncthreads();
+    if (pf) {
+      commit(nt);
+      __syncthreads();
+      if (t0 + TCH < t_hi) fetch(t0 + TCH, min(TCH, t_hi - t0 - TCH));
+    } else {
     // flattened over (token, row) so that a thread's loads are independent and many are in flight at once; 16-byte loads
     // where the rows allow
     if (in_vec) {
@@ -681,6 +740,7 @@ __global__ void __launch_bounds__(128) linear_scan_tile_kernel(ScanArgs a) {
     }
     if (KIND == 1 && threadIdx.x < nt) as[threadIdx.x] = expf(a.decay[(int64_t)(s.q0 + t0 + threadIdx.x) * a.ldd + h]);
     __syncthreads();
+    }
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const float at = KIND == 1 ? as[tt] : a_const;
