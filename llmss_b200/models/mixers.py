@@ -145,7 +145,7 @@ class BiasedAttention:
         self.width, self.heads, self.kv_heads, self.dim, self.vdim, self.taps = width, heads, kv_heads, dim, vdim, taps
         self.scale, self.temp_coef, self.temp_every, self.bias_max, self.eps = scale, temp_coef, temp_every, bias_max, eps
         self.n_qkv = heads * dim + kv_heads * dim + kv_heads * vdim
-        self.w_rows = self.b_rows = self.conv_w = self.q_norm = self.k_norm = self.dist_bias = self.w_o = None
+        self.w_rows = self.b_rows = self.conv_w = self.q_norm = self.k_norm = self.dist_bias = self.dist_bias_scaled = self.w_o = None
         self.off = 0
 
     def state_shapes(self):
@@ -163,6 +163,8 @@ class BiasedAttention:
         self.conv_w = torch.cat([cq, ck, cv], dim=0).contiguous()
         self.q_norm, self.k_norm, self.w_o = q_norm, k_norm, w_o.contiguous()
         self.dist_bias = ops.distance_bias_table(rel.float().cpu(), self.bias_max).to(w_o.device)   # [heads, bias_max + 1] 32-bit
+        # the same table in raw-score units, for the tensor-core kernels that add it before their one multiply by the scale
+        self.dist_bias_scaled = (self.dist_bias / self.scale).contiguous() if self.scale > 0 else None
 
     def in_rows(self):
         return self.w_rows
@@ -187,7 +189,8 @@ class BiasedAttention:
             q = ops.qknorm_kv_write(qkv, H, G, D, Dv, self.q_norm, self.k_norm, self.eps, self.temp_coef, self.temp_every,
                                     batch.positions, batch.slot_mapping, lc.k, lc.v, out_dtype=dtype)
         with trace("attention_bias"):
-            ctx = ops.attention_bias(q, lc.k, lc.v, batch, H, G, D, Dv, self.scale, self.dist_bias, gate=gate, out_dtype=dtype)
+            ctx = ops.attention_bias(q, lc.k, lc.v, batch, H, G, D, Dv, self.scale, self.dist_bias, gate=gate, out_dtype=dtype,
+                                     bias_over_scale=self.dist_bias_scaled)
         with trace("gemm_out"):
             return ops.linear(ctx, self.w_o, out_dtype=F32)
 

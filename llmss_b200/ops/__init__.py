@@ -303,12 +303,13 @@ def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, 
                      slot_mapping, k_cache, v_cache, out_dtype)
 
 
-def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None):
-    """Causal paged attention with separate key / value sizes, a per-head distance bias table and an output gate."""
+def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None):
+    """Causal paged attention with separate key / value sizes, a per-head distance bias table and an output gate.
+    ``bias_over_scale``: dist_bias / scale, kept by the caller for the tensor-core kernels (derived per call if absent)."""
     if _cuda(q):
         from . import cuda_impl as cu
 
-        return cu.attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate, out_dtype)
+        return cu.attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate, out_dtype, bias_over_scale)
     return ref.attention_bias(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q, hq, hkv, dk, dv, scale,
                               dist_bias, gate, out_dtype)
 

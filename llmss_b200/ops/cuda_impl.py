@@ -749,16 +749,14 @@ def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, 
 
 
 _BIAS_TC = os.environ.get("LLMSS_ATTN_BIAS_TC", "1") == "1"
-_BIAS_OVER_SCALE = {}
 
 
-def _bias_over_scale(dist_bias, scale):
-    """The distance table in the units of the raw scores (the tensor-core kernel adds it before its one multiply)."""
-    key = (dist_bias.data_ptr(), float(scale))
-    t = _BIAS_OVER_SCALE.get(key)
-    if t is None:
-        t = _BIAS_OVER_SCALE[key] = (dist_bias.float() / float(scale)).contiguous()
-    return t
+def _bias_over_scale(dist_bias, scale, given=None):
+    """The distance table in the units of the raw scores (the tensor-core kernels add it before their one multiply).  Callers
+    that keep the table (a model layer) pass it as ``given``; otherwise it is derived per call."""
+    if given is not None:
+        return given
+    return (dist_bias.float() / float(scale)).contiguous()
 
 
 def attention_bias_uses_tc(dtype, dk: int, dv: int, block_size: int, scale: float) -> bool:
@@ -768,7 +766,7 @@ def attention_bias_uses_tc(dtype, dk: int, dv: int, block_size: int, scale: floa
             and _lib.has("llmss_attn_prefill_paged_bias"))
 
 
-def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None):
+def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None):
     lib = _lib.load()
     T = q.shape[0]
     dt = q.dtype
@@ -781,7 +779,7 @@ def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias
             # one query per sequence: the split-KV decode kernel (the q heads of a group are its MMA rows), then the gate
             splits = batch.decode_splits or decode_splits(batch.num_seqs, hq, hkv, dk, batch.max_kv, dt, bs)
             attn_decode(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, out, hq, hkv, dk, scale, splits,
-                        bias_over_scale=_bias_over_scale(dist_bias, scale))
+                        bias_over_scale=_bias_over_scale(dist_bias, scale, bias_over_scale))
             if gate is not None:
                 _lib.check(lib.llmss_head_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), T, hq, dv, _DT[dt], _stream()),
                            "llmss_head_gate")
@@ -791,7 +789,7 @@ def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias
                                                batch.block_tables.shape[1], _ptr(batch.seq_lens), _ptr(out), out.stride(0),
                                                _ptr(batch.cu_q), batch.num_seqs, max(1, batch.max_q), T, hq, hkv, dk,
                                                k_cache.shape[2], k_cache.shape[0], float(scale), _DT[dt],
-                                               _ptr(_bias_over_scale(dist_bias, scale)), dist_bias.shape[1], _ptr(gate),
+                                               _ptr(_bias_over_scale(dist_bias, scale, bias_over_scale)), dist_bias.shape[1], _ptr(gate),
                                                gate.stride(0) if gate is not None else 0, _stream())
         _lib.check(rc, "llmss_attn_prefill_paged_bias")
         _count()
