@@ -473,7 +473,6 @@ __global__ void __launch_bounds__(128) linear_scan_tile_kernel(ScanArgs a) {
   constexpr int row = RG * TSTR;                 // floats per staged token
   const int cg = threadIdx.x / RG, rg = threadIdx.x % RG;
   const int i0 = rg * 8, c0 = cg * 8;            // first key row / first column (inside the slice) of this thread
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   float* qs = sm;
   float* ks = qs + TCH * row;
   float* as = ks + TCH * row;                                   // [TCH][row] (kind 2) or [TCH] (kind 1)
@@ -901,10 +900,6 @@ LLMSS_API int llmss_ssm_dt(const float* raw, int64_t ldr, const float* dt_bias, 
   return 0;
 }
 
-static int g_scan_tile = 1;
-// 0: every key size runs the column-per-thread kernel (A/B aid and the form tests compare against)
-LLMSS_API int llmss_linear_scan_set_tile(int on) { g_scan_tile = on; return 0; }
-
 LLMSS_API int64_t llmss_linear_scan_scratch_floats(int B, int heads, int dk, int dv, int max_q, int chunk) {
   const int nch = chunk > 0 ? (max_q + chunk - 1) / chunk : 0;
   return (int64_t)B * heads * ((int64_t)dv * dk + (int64_t)nch * ((int64_t)dv * dk + dk));
@@ -931,7 +926,7 @@ LLMSS_API int llmss_linear_scan(const float* q, int64_t ldq, const float* k, int
   a.old_copy = scratch;
   a.chunk_state = scratch != nullptr ? scratch + (int64_t)B * heads * dv * dk : nullptr;
   a.chunk_decay = scratch != nullptr ? a.chunk_state + (int64_t)B * a.nch * heads * dv * dk : nullptr;
-  if (dk > 32 && dk <= 128 && g_scan_tile) {
+  if (dk > 32 && dk <= 128) {
     // 8 x 8 register tiles: RG row groups of 8 key rows, value columns in groups of 8
     const int rg = dk <= 64 ? 8 : 16;
     a.R = rg;
